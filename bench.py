@@ -1,0 +1,393 @@
+"""Benchmark of the neighborhood-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch of synthetic input: a
+fused forward + backward call for every variant of the workload.  The default
+workload is the NAT-stage configuration: na2d bf16, B=32, 56x56, 4 heads,
+D=32, kernel 7x7, dilation 1 and dilation 4 (two calls per step).
+
+Prints ONE JSON line.  ``value`` is whole-job effective TFLOP/s (algorithmic
+FLOPs: forward 4*B*H*N*K_vol*D, backward 2.5x that) with inputs resident in
+HBM; ``e2e`` is the same metric through the public API with pinned HOST
+buffers, host<->device copies inside the timed region.  ``roofline`` is for
+the kernel with the largest share of device time, measured live with CUDA
+events recorded by the library around each of its launches.
+
+With ``--gpus N`` (launched by torchrun, one rank per GPU) every rank runs the
+same per-GPU batch (weak scaling, no data-path collective: the batch x head
+shards are independent); time is the max over ranks.
+
+``--impl reference`` times the CPU restatement of the reference's pure backend
+(the MLX array library it needs does not install on Linux) on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _sub in ("natten-mlx_b200", "oracle"):
+    _p = os.path.join(ROOT, _sub)
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+
+# ---------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------
+WORKLOADS = {
+    # name: dict(rank, shape [B, spatial..., Hq, D], heads_kv, kernel, dilation variants, causal, dtype)
+    "na2d_nat_stage": dict(shape=(32, 56, 56, 4, 32), heads_kv=4, kernel=(7, 7), dilations=[(1, 1), (4, 4)],
+                           causal=(False, False), dtype="bf16",
+                           label="na2d bf16 B=32 56x56 H=4 D=32 K=7x7 dilation {1,4} fwd+bwd"),
+    "na3d_video": dict(shape=(2, 32, 96, 96, 16, 64), heads_kv=16, kernel=(3, 7, 7), dilations=[(1, 2, 2)],
+                       causal=(True, False, False), dtype="bf16",
+                       label="na3d bf16 B=2 T=32 96x96 H=16 D=64 K=(3,7,7) causal-T dilation (1,2,2) fwd+bwd"),
+    "na1d_parity": dict(shape=(2, 64, 4, 32), heads_kv=4, kernel=(7,), dilations=[(1,)], causal=(False,),
+                        dtype="f32", label="na1d fp32 B=2 L=64 H=4 D=32 K=7 fwd+bwd"),
+}
+DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
+
+
+def kvol(w):
+    v = 1
+    for k in w["kernel"]:
+        v *= k
+    return v
+
+
+def flops_fwd(w):
+    b, hq, d = w["shape"][0], w["shape"][-2], w["shape"][-1]
+    n = 1
+    for e in w["shape"][1:-2]:
+        n *= e
+    return 4.0 * b * hq * n * kvol(w) * d
+
+
+def flops_step(w):
+    return 3.5 * flops_fwd(w) * len(w["dilations"])
+
+
+def tensor_bytes(w, heads=None):
+    n = 1
+    for e in w["shape"][:-2]:
+        n *= e
+    esz = torch.tensor([], dtype=DTYPES[w["dtype"]]).element_size()
+    return n * (heads if heads is not None else w["shape"][-2]) * w["shape"][-1] * esz
+
+
+def lse_bytes(w):
+    n = 1
+    for e in w["shape"][:-1]:
+        n *= e
+    return n * 4
+
+
+def algorithmic_bytes(w):
+    """Compulsory HBM traffic per launch of each kernel (one variant)."""
+    tq, tkv, tl = tensor_bytes(w), tensor_bytes(w, w["heads_kv"]), lse_bytes(w)
+    fwd = tq + 2 * tkv + tq + tl                      # read q,k,v ; write out,lse
+    bwd_q = tq + 2 * tkv + tq + tq + tl + tq + tl     # read q,k,v,out,dout,lse ; write dq,delta
+    bwd_kv = tq + 2 * tkv + tq + 2 * tl + 2 * tkv     # read q,k,v,dout,lse,delta ; write dk,dv
+    return {"fused_fwd": fwd, "fused_bwd_q": bwd_q, "fused_bwd_kv": bwd_kv,
+            "fna_fwd_sm100": fwd, "fna_bwd_dq_sm100": bwd_q, "fna_bwd_dkv_sm100": bwd_kv,
+            "fna_bwd_prep_sm100": 2 * tq + 2 * tl}
+
+
+def make_inputs(w, seed, device, pinned=False):
+    """q, k, v and the output cotangent: iid N(0,1) from a fixed seed, cast to the dtype."""
+    gen = torch.Generator().manual_seed(seed)
+    dt = DTYPES[w["dtype"]]
+    kv_shape = w["shape"][:-2] + (w["heads_kv"], w["shape"][-1])
+    out = []
+    for shape in (w["shape"], kv_shape, kv_shape, w["shape"]):
+        t = torch.randn(shape, generator=gen, dtype=torch.float32).to(dt)
+        t = t.pin_memory() if pinned else t.to(device)
+        out.append(t)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        with open(self.path) as fh:
+            for line in fh:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 9:
+                    continue
+                try:
+                    sm.append(float(parts[1])); mx.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, parts[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# the reference arm / CPU baseline: the oracle on the host cores
+# ---------------------------------------------------------------------------
+def cpu_sample_step(w, batch):
+    """Forward + backward of every variant on `batch` samples with the CPU oracle (float32)."""
+    import natten_oracle as oracle
+    wb = dict(w, shape=(batch,) + tuple(w["shape"][1:]))
+    total = 0.0
+    for vi, dil in enumerate(w["dilations"]):
+        q, k, v, cot = (t.float() for t in make_inputs(wb, 1234 + vi, "cpu"))
+        t0 = time.perf_counter()
+        oracle.grads(lambda a, b, c: oracle.na(a, b, c, w["kernel"], 1, dil, w["causal"]), [q, k, v], cot)
+        total += time.perf_counter() - t0
+    return total
+
+
+def cpu_sample_batch(w):
+    # keep the K_vol-fold gather of the CPU path near a few hundred MB
+    per_sample = tensor_bytes(dict(w, shape=(1,) + tuple(w["shape"][1:]), dtype="f32")) * kvol(w)
+    return max(1, min(w["shape"][0], int(400e6 // max(per_sample, 1))))
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    batch = cpu_sample_batch(w)
+    for _ in range(args.warmup):
+        cpu_sample_step(w, batch)
+    t = sum(cpu_sample_step(w, batch) for _ in range(args.steps))
+    ms = t / args.steps * 1e3
+    tflops = flops_step(w) * batch / w["shape"][0] / (ms * 1e-3) / 1e12
+    sample = f"{batch} of {w['shape'][0]} samples per step, float32, both passes, every variant"
+    line = {
+        "impl": "reference", "metric": "na_fwd_bwd_effective_tflops", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["label"], "note": "CPU restatement of the reference's pure backend (torch CPU ops)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def run_ours(args, w, rank, world, local_rank):
+    import torch.distributed as dist
+    import natten_mlx_b200 as nb
+    from natten_mlx_b200 import _lib
+    from natten_mlx_b200._core import cuda as backend
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device for the default arm (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    rank_nd = len(w["shape"]) - 3
+    one, nvar = (1,) * rank_nd, len(w["dilations"])
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peaks = json.load(fh)
+    except OSError:
+        pass
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
+
+    # device-resident inputs, one set per variant so that no variant finds its inputs in L2
+    dev_in = [make_inputs(w, 1234 + vi, dev) for vi in range(nvar)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step_device():
+        for (q, k, v, cot), dil in zip(dev_in, w["dilations"]):
+            out, lse = backend.fused_forward(q, k, v, w["kernel"], one, dil, w["causal"], None)
+            backend.fused_backward(q, k, v, out, lse, cot, None, w["kernel"], one, dil, w["causal"], None)
+
+    # end-to-end: pinned host buffers -> device -> public API forward + backward -> host
+    host_in = [make_inputs(w, 1234 + vi, dev, pinned=True) for vi in range(nvar)]
+    host_out = [[torch.empty_like(t).pin_memory() for t in (hi[0], hi[0], hi[1], hi[2])] for hi in host_in]
+    stage = [[torch.empty(t.shape, dtype=t.dtype, device=dev) for t in hi] for hi in host_in]
+    fused = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[rank_nd]
+    h2d = sum(t.numel() * t.element_size() for hi in host_in for t in hi)
+    d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
+
+    def step_e2e():
+        for hi, ho, st, dil in zip(host_in, host_out, stage, w["dilations"]):
+            for s, h in zip(st, hi):
+                s.copy_(h, non_blocking=True)
+            q, k, v = (t.requires_grad_(True) for t in st[:3])
+            out = fused(q, k, v, kernel_size=w["kernel"], dilation=dil, is_causal=w["causal"])
+            dq, dk, dv = torch.autograd.grad(out, (q, k, v), st[3])
+            for h, d in zip(ho, (out.detach(), dq, dk, dv)):
+                h.copy_(d, non_blocking=True)
+            for t in st[:3]:
+                t.requires_grad_(False)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps, trace):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        barrier()
+        if trace:
+            _lib.trace_report()
+            _lib.trace_enable(True)
+        for a, b in evs:
+            flush.zero_()                       # evict L2 between timed iterations
+            a.record()
+            step_fn()
+            b.record()
+        barrier()
+        if trace:
+            _lib.trace_enable(False)
+        ms = sum(a.elapsed_time(b) for a, b in evs)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    ms_dev = timed(step_device, args.steps, trace=True)
+    launches = _lib.launch_count() - launches0
+    trace = _lib.trace_report()
+    path = _lib.last_path()
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps, trace=False)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # the traced timings include the event overhead, so recompute ms_dev untraced as the headline
+    ms_plain = timed(step_device, args.steps, trace=False)
+
+    if rank != 0:
+        return
+    total_flops = flops_step(w) * world
+    value = total_flops / (ms_plain * 1e-3) / 1e12
+    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
+
+    alg = algorithmic_bytes(w)
+    roofline = None
+    if trace:
+        name, (n, ms_total) = max(trace.items(), key=lambda kv: kv[1][1])
+        per_launch_ms = ms_total / n
+        share = ms_total / sum(v[1] for v in trace.values())
+        if name in alg:
+            achieved = alg[name] / (per_launch_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                        "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                        "launch_ms": per_launch_ms, "share_of_device_time": share,
+                        "algorithmic_bytes_per_launch": alg[name]}
+    kernels = {k: {"launches": n, "ms_per_launch": ms / n} for k, (n, ms) in sorted(trace.items())}
+
+    cpu = None
+    if world == 1:
+        torch.set_num_threads(os.cpu_count() or 1)
+        batch = cpu_sample_batch(w)
+        cpu_sample_step(w, batch)
+        t_cpu, reps = 0.0, 0
+        while t_cpu < 10.0 and reps < 20:
+            t_cpu += cpu_sample_step(w, batch)
+            reps += 1
+        cpu_tflops = flops_step(w) * batch / w["shape"][0] * reps / t_cpu / 1e12
+        cpu = {"value": cpu_tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{batch} of {w['shape'][0]} samples, {reps} repetitions, float32 CPU restatement of the "
+                         "reference's pure backend, forward+backward of every variant"}
+
+    line = {
+        "metric": "na_fwd_bwd_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_plain, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["label"], "calls_per_step": nvar, "per_gpu_batch": w["shape"][0],
+                   "global_batch": w["shape"][0] * world, "parallelism": f"batch-sharded x{world}, no collective",
+                   "l2": "256 MiB buffer written between timed iterations; separate inputs per variant",
+                   "kernel_family": path, "flops_model": "fwd 4*B*H*N*K_vol*D, bwd 2.5x fwd",
+                   "ms_per_call_fwd_bwd": ms_plain / nvar},
+        "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="na2d_nat_stage", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, w, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
