@@ -132,9 +132,11 @@ int make_geo(const natten_b200_geom* in, Geo* g) {
         int start, hi;
         axis_window(p, g->ge[a], g->K[a], g->dl[a], g->ca[a], start, hi);
         const int lo = start < 0 ? (start % g->dl[a] + g->dl[a]) % g->dl[a] : start;
-        if (lo < hi && (lo < g->ko[a] || hi > g->ko[a] + g->ke[a]))
+        if (lo >= hi) continue;
+        const int last = lo + ((hi - 1 - lo) / g->dl[a]) * g->dl[a];  // last key on the window's lattice
+        if (lo < g->ko[a] || last >= g->ko[a] + g->ke[a])
           return set_error(NATTEN_B200_EINVAL,
-                           "axis %d: query %d needs keys [%d, %d) but the local key slab is [%d, %d)", i, p, lo, hi,
+                           "axis %d: query %d needs keys [%d, %d] but the local key slab is [%d, %d)", i, p, lo, last,
                            g->ko[a], g->ko[a] + g->ke[a]);
       }
     }

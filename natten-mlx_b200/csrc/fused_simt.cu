@@ -335,8 +335,13 @@ __device__ __forceinline__ int inverse_slot(const Geo& g, int a, int ext, int x,
 // One warp per (key, kv head).  Pass 1 walks the candidate queries, keeps the
 // ones whose window holds the key and stores (P, dS, row ids) in shared
 // memory; pass 2 forms dV = sum P * dO and dK = scale * sum dS * Q.
-// Shared memory per warp: k [D], v [D], P [cap], dS [cap], out-row [cap],
-// q-row [cap] with cap = rep * K_vol.
+// A key near a clamped edge is addressed by more queries than the kernel has
+// slots (every edge query's window is pulled inward over it), so the lists are
+// sized for a window of kKvWindow candidates and the candidates are walked
+// window by window.
+// Shared memory per warp: k [D], v [D], and P, dS, out-row, q-row of kKvWindow
+// entries each.
+constexpr int kKvWindow = 512;
 template <typename T, int CH>
 __global__ void __launch_bounds__(kWarps * 32)
 k_fused_bwd_kv(Geo g, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
@@ -345,7 +350,7 @@ k_fused_bwd_kv(Geo g, const T* __restrict__ q, const T* __restrict__ k, const T*
                long long n_rows) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int cap = g.rep * g.kvol;
+  const int cap = kKvWindow;
   const int Dp = (g.D + 3) & ~3;
   const size_t per_warp = (size_t)Dp * 8 + (size_t)cap * 16;
   unsigned char* base = smem_raw + (size_t)warp * ((per_warp + 15) & ~(size_t)15);
@@ -357,7 +362,9 @@ k_fused_bwd_kv(Geo g, const T* __restrict__ q, const T* __restrict__ k, const T*
   int* qrow = orow + cap;
   const bool vec = CH != 1;
   const int chunks = g.D / CH;
-  const int C0 = 2 * g.K[0] - 1, C1 = 2 * g.K[1] - 1, C2 = 2 * g.K[2] - 1;
+  // a query can sit up to K lattice steps from a key it addresses: an even
+  // kernel pulled inward at the far edge does not reach the query itself
+  const int C0 = 2 * g.K[0] + 1, C1 = 2 * g.K[1] + 1, C2 = 2 * g.K[2] + 1;
   const int n_cand = g.rep * C0 * C1 * C2;
 
   for (long long row = (long long)blockIdx.x * kWarps + warp; row < n_rows;
@@ -376,62 +383,67 @@ k_fused_bwd_kv(Geo g, const T* __restrict__ q, const T* __restrict__ k, const T*
       vs[i] = to_f<T>(v[row * g.D + i]);
     }
     __syncwarp();
-    int count = 0;
-    for (int c0 = 0; c0 < n_cand; c0 += 32) {
-      const int c = c0 + lane;
-      bool ok = c < n_cand;
-      float p = 0.f, ds = 0.f;
-      int orow_i = 0, qrow_i = 0;
-      if (ok) {
-        int u = c;
-        const int m2 = u % C2 - (g.K[2] - 1); u /= C2;
-        const int m1 = u % C1 - (g.K[1] - 1); u /= C1;
-        const int m0 = u % C0 - (g.K[0] - 1); u /= C0;
-        const int h = hk * g.rep + u;
-        int o0, o1, o2;
-        ok = inverse_slot(g, 0, ext[0], x0, m0, o0) >= 0 && inverse_slot(g, 1, ext[1], x1, m1, o1) >= 0 &&
-             inverse_slot(g, 2, ext[2], x2, m2, o2) >= 0;
-        if (ok) {
-          const long long ol = ((long long)o0 * g.out[1] + o1) * g.out[2] + o2;
-          const long long ql = ((long long)(o0 * g.st[0]) * g.qe[1] + o1 * g.st[1]) * g.qe[2] + o2 * g.st[2];
-          const long long orl = ((long long)b * g.n_out + ol) * g.Hq + h;
-          const long long qrl = ((long long)b * g.n_q + ql) * g.Hq + h;
-          orow_i = (int)orl;
-          qrow_i = (int)qrl;
-          p = __expf(g.scale * dot_smem<T>(ks, q + qrl * g.D, g.D, vec) - lse[orl]);
-          ds = p * (dot_smem<T>(vs, dout + orl * g.D, g.D, vec) - delta[orl]);
-        }
-      }
-      const unsigned ballot = __ballot_sync(0xffffffffu, ok);
-      if (ok) {
-        const int pos = count + __popc(ballot & ((1u << lane) - 1u));
-        ps[pos] = p;
-        dss[pos] = ds;
-        orow[pos] = orow_i;
-        qrow[pos] = qrow_i;
-      }
-      count += __popc(ballot);
-    }
-    __syncwarp();
     const ChunkMap cm = chunk_map(chunks, lane);
-    for (int c0 = 0; c0 < chunks; c0 += cm.cp) {
-      const int c = c0 + cm.c;
+    for (int cg = 0; cg < chunks; cg += cm.cp) {
+      const int cc = cg + cm.c;
       float av[CH], ak[CH];
 #pragma unroll
       for (int i = 0; i < CH; ++i) { av[i] = 0.f; ak[i] = 0.f; }
-      if (c < chunks) {
-        for (int s = cm.sg; s < count; s += cm.G) {
-          axpy_row<T, CH>(ps[s], dout + (long long)orow[s] * g.D + c * CH, av);
-          axpy_row<T, CH>(dss[s], q + (long long)qrow[s] * g.D + c * CH, ak);
+      // candidates are taken in windows of kKvWindow so that the lists always fit
+      for (int w0 = 0; w0 < n_cand; w0 += kKvWindow) {
+        const int w1 = w0 + kKvWindow < n_cand ? w0 + kKvWindow : n_cand;
+        int count = 0;
+        for (int c0 = w0; c0 < w1; c0 += 32) {
+          const int c = c0 + lane;
+          bool ok = c < w1;
+          float p = 0.f, ds = 0.f;
+          int orow_i = 0, qrow_i = 0;
+          if (ok) {
+            int u = c;
+            const int m2 = u % C2 - g.K[2]; u /= C2;
+            const int m1 = u % C1 - g.K[1]; u /= C1;
+            const int m0 = u % C0 - g.K[0]; u /= C0;
+            const int h = hk * g.rep + u;
+            int o0, o1, o2;
+            ok = inverse_slot(g, 0, ext[0], x0, m0, o0) >= 0 && inverse_slot(g, 1, ext[1], x1, m1, o1) >= 0 &&
+                 inverse_slot(g, 2, ext[2], x2, m2, o2) >= 0;
+            if (ok) {
+              const long long ol = ((long long)o0 * g.out[1] + o1) * g.out[2] + o2;
+              const long long ql = ((long long)(o0 * g.st[0]) * g.qe[1] + o1 * g.st[1]) * g.qe[2] + o2 * g.st[2];
+              const long long orl = ((long long)b * g.n_out + ol) * g.Hq + h;
+              const long long qrl = ((long long)b * g.n_q + ql) * g.Hq + h;
+              orow_i = (int)orl;
+              qrow_i = (int)qrl;
+              p = __expf(g.scale * dot_smem<T>(ks, q + qrl * g.D, g.D, vec) - lse[orl]);
+              ds = p * (dot_smem<T>(vs, dout + orl * g.D, g.D, vec) - delta[orl]);
+            }
+          }
+          const unsigned ballot = __ballot_sync(0xffffffffu, ok);
+          if (ok) {
+            const int pos = count + __popc(ballot & ((1u << lane) - 1u));
+            ps[pos] = p;
+            dss[pos] = ds;
+            orow[pos] = orow_i;
+            qrow[pos] = qrow_i;
+          }
+          count += __popc(ballot);
         }
+        __syncwarp();
+        if (cc < chunks) {
+          for (int s = cm.sg; s < count; s += cm.G) {
+            axpy_row<T, CH>(ps[s], dout + (long long)orow[s] * g.D + cc * CH, av);
+            axpy_row<T, CH>(dss[s], q + (long long)qrow[s] * g.D + cc * CH, ak);
+          }
+        }
+        __syncwarp();
       }
       reduce_groups<CH>(av, cm.cp);
       reduce_groups<CH>(ak, cm.cp);
-      if (cm.sg == 0 && c < chunks) {
+      if (cm.sg == 0 && cc < chunks) {
 #pragma unroll
         for (int i = 0; i < CH; ++i) ak[i] *= g.scale;
-        store_chunk<T, CH>(dv + row * g.D + c * CH, av);
-        store_chunk<T, CH>(dk + row * g.D + c * CH, ak);
+        store_chunk<T, CH>(dv + row * g.D + cc * CH, av);
+        store_chunk<T, CH>(dk + row * g.D + cc * CH, ak);
       }
     }
     __syncwarp();
@@ -578,8 +590,7 @@ int bwd_impl(const Geo& g, const FusedArgs& a, cudaStream_t s) {
         (const T*)a.out, a.lse, (const T*)a.dout, a.dlse, (T*)a.dq, delta, rows));
   }
   {
-    const size_t cap = (size_t)g.rep * g.kvol;
-    const size_t smem = kWarps * align16((size_t)Dp * 8 + cap * 16);
+    const size_t smem = kWarps * align16((size_t)Dp * 8 + (size_t)kKvWindow * 16);
     if (int rc = opt_in_smem(k_fused_bwd_kv<T, CH>, smem)) return rc;
     const long long krows = (long long)g.B * g.n_kv * g.Hkv;
     NB_LAUNCH("fused_bwd_kv", s, k_fused_bwd_kv<T, CH><<<blocks_for_rows(krows), kWarps * 32, smem, s>>>(

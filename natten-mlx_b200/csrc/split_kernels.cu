@@ -182,7 +182,7 @@ k_weighted_sum(Geo g, const T* __restrict__ w, const T* __restrict__ y, T* __res
 // inverse_sum
 // ---------------------------------------------------------------------------
 // For key coordinate x on one axis, candidate queries are x + m*dil for
-// |m| < K; a candidate counts when it lies on the stride lattice inside the
+// |m| <= K; a candidate counts when it lies on the stride lattice inside the
 // local query slab and its window holds x.  Returns the slot or -1.
 __device__ __forceinline__ int inverse_slot(const Geo& g, int a, int ext, int x, int m, int& o) {
   const int p = x + m * g.dl[a];
@@ -220,15 +220,15 @@ k_inverse_sum(Geo g, const T* __restrict__ w, const T* __restrict__ src, T* __re
 #pragma unroll
     for (int i = 0; i < CH; ++i) acc[i] = 0.f;
     if (x0 < ext[0] && x1 < ext[1] && x2 < ext[2]) {
-      for (int m0 = 1 - g.K[0]; m0 < g.K[0]; ++m0) {
+      for (int m0 = -g.K[0]; m0 <= g.K[0]; ++m0) {
         int o0;
         const int s0 = inverse_slot(g, 0, ext[0], x0, m0, o0);
         if (s0 < 0) continue;
-        for (int m1 = 1 - g.K[1]; m1 < g.K[1]; ++m1) {
+        for (int m1 = -g.K[1]; m1 <= g.K[1]; ++m1) {
           int o1;
           const int s1 = inverse_slot(g, 1, ext[1], x1, m1, o1);
           if (s1 < 0) continue;
-          for (int m2 = 1 - g.K[2]; m2 < g.K[2]; ++m2) {
+          for (int m2 = -g.K[2]; m2 <= g.K[2]; ++m2) {
             int o2;
             const int s2 = inverse_slot(g, 2, ext[2], x2, m2, o2);
             if (s2 < 0) continue;

@@ -311,9 +311,8 @@ def test_config_na2d_varlen_gqa_extra_tokens_reduced():
         close_lowp(a, b, name)
     # padding is exactly zero in outputs and gradients
     for b, (h, w) in enumerate(sizes):
-        assert o[b, h:].abs().max() == 0 and o[b, :, w:].abs().max() == 0
-        for t in g[:3]:
-            assert t[b, h:].abs().max() == 0 and t[b, :, w:].abs().max() == 0
+        for t in (o,) + tuple(g[:3]):
+            assert t[b, h:].abs().sum() == 0 and t[b, :, w:].abs().sum() == 0
 
 
 # ---------------------------------------------------------------------------
