@@ -177,6 +177,25 @@ int natten_b200_fused_forward(const natten_b200_geom* g, const void* q, const vo
                               const void* v, const void* k_extra, const void* v_extra,
                               void* out, float* lse, void* stream);
 
+/*
+ * 1 when a tensor-core kernel launched by this library on the current device
+ * gave up on one of its bounded waits since the last call (its results are
+ * then invalid), 0 otherwise.  Synchronises with the device.  Stands where the
+ * reference turns a failed accelerated kernel into a silent fallback
+ * (src/natten_mlx/_core/fast_metal.py:2003-2016): here it is reported instead.
+ */
+int natten_b200_kernel_status(void);
+
+/* Diagnostic for tests: when device_buffer is not NULL the tensor-core forward
+ * writes the raw QK^T tile of its first work item there
+ * ([chunks][128][padded columns] float32).  No counterpart in the reference. */
+void natten_b200_debug_set_s_dump(float* device_buffer);
+
+/* Writes a one-line description of the tensor-core tiling chosen for a
+ * geometry (or why it is unsupported) into buf.  Needs no GPU.  Takes the
+ * place of the reference's tuning tables (src/natten_mlx/_core/_forward_tuning.py:11-34). */
+int natten_b200_describe_plan(const natten_b200_geom* g, char* buf, size_t cap);
+
 /* Bytes of scratch natten_b200_fused_backward needs for this geometry. */
 size_t natten_b200_fused_backward_scratch_bytes(const natten_b200_geom* g);
 

@@ -323,6 +323,18 @@ int natten_b200_fused_backward(const natten_b200_geom* gi, const void* q, const 
   return run_fused_backward_simt(g, gi->dtype, a, (cudaStream_t)stream);
 }
 
+int natten_b200_kernel_status(void) { return sm100_read_status(); }
+
+void natten_b200_debug_set_s_dump(float* device_buffer) { sm100_set_debug_s(device_buffer); }
+
+int natten_b200_describe_plan(const natten_b200_geom* gi, char* buf, size_t cap) {
+  Geo g;
+  if (int rc = make_geo(gi, &g)) return rc;
+  if (buf == nullptr || cap == 0) return set_error(NATTEN_B200_EINVAL, "describe_plan: null buffer");
+  sm100_describe_plan(g, gi->dtype, buf, cap);
+  return NATTEN_B200_OK;
+}
+
 int natten_b200_merge_forward(int32_t dtype, int64_t rows, int32_t head_dim, const void* o0,
                               const float* l0, const void* o1, const float* l1, void* out,
                               float* lse, void* stream) {

@@ -1,17 +1,240 @@
-// Tensor-core (tcgen05 + TMEM + TMA) fused neighborhood attention for sm_100a.
+// Tensor-core fused neighborhood attention, forward pass, for sm_100a.
+//
+// A CTA owns one (batch, kv head, dilation class, query tile).  Dilation is
+// removed up front: the queries p = i*d + g of one residue class g attend only
+// to keys of the same class, so each class is a dilation-1 problem on a
+// strided view and gets its own TMA tensor maps.  The 128 rows of the tile
+// are (heads sharing the kv head) x (tile positions).  The keys every row of
+// the tile can address form a box; the box is walked in chunks of at most a
+// few hundred keys.  Per chunk:
+//   TMA warp     K/V chunk -> shared memory (zero fill outside the tensor)
+//   MMA warp     S = Q K^T   (tcgen05.mma, operands in smem, S in TMEM)
+//   4 softmax warps   S -> registers, per-row window/causal mask from a
+//                bitmap, online softmax in base 2, P (bf16/f16) -> TMEM over S
+//   MMA warp     O += P V    (A = P from TMEM, B = V as an MN-major operand)
+// and at the end of the tile the softmax warps scale O by 1/l and write
+// out and the log-sum-exp.  Math as in src/natten_mlx/_core/pure.py:155-255
+// with the LSE of src/natten_mlx/functional.py:368-372.
+#include <cuda.h>
+#include <math.h>
+#include <stdio.h>
+
+#include <mutex>
+
 #include "fna_sm100.cuh"
+#include "sm100_ptx.cuh"
 
 namespace nb {
+namespace {
 
-bool sm100_forward_supported(const Geo&, int) { return false; }
-bool sm100_backward_supported(const Geo&, int) { return false; }
-const char* sm100_unsupported_reason(const Geo&, int) { return "tensor-core kernels are not built yet"; }
-int run_fused_forward_sm100(const Geo&, int, const FusedArgs&, cudaStream_t) {
-  return set_error(NATTEN_B200_EINVAL, "tensor-core forward is not available");
-}
-int run_fused_backward_sm100(const Geo&, int, const FusedArgs&, cudaStream_t) {
-  return set_error(NATTEN_B200_EINVAL, "tensor-core backward is not available");
-}
-size_t fused_backward_scratch_sm100(const Geo&, int) { return 0; }
+using namespace sm100;
 
+constexpr int kMaxClasses = 16;
+constexpr int kTileM = 128;
+constexpr int kMaxCols = 384;            // S columns per chunk (TMEM: S at 0, O at 384)
+constexpr int kOCol = 384;
+constexpr int kMaxGroups = kMaxCols / 16;
+constexpr int kMaxWords = kMaxCols / 32;
+constexpr int kThreads = 192;            // 4 softmax warps, 1 TMA warp, 1 MMA warp
+
+struct alignas(64) TmaMaps {
+  CUtensorMap q[kMaxClasses];
+  CUtensorMap k[kMaxClasses];
+  CUtensorMap v[kMaxClasses];
+};
+
+struct FwdParams {
+  int B, Hq, Hkv, rep, D;
+  int rank;              // spatial rank of the tensors (tensor-map rank = rank + 2)
+  int L[3], K[3], dl[3], ca[3];
+  int T[3];              // query tile extents in class coordinates
+  int hpt, P;            // heads per tile, positions per tile (hpt * P == 128)
+  int box[3];            // key box extents
+  int chunk_axis, R, cchunks, n_chunks, inner, n_cols, n_pad, n_split, n_half;
+  int dblk, ndblk, row_bytes, layout_type;
+  int q_stages, kv_stages;
+  int tiles[3];
+  long long n_work;
+  float scale_log2;
+  uint32_t idesc_qk, idesc_pv;
+  int is_bf16;
+  void* out;
+  float* lse;
+  int* status;
+  float* dbg_s;          // optional [n_chunks of the first work item][128][n_pad] raw S dump
+};
+
+// ---------------------------------------------------------------------------
+// host: planning
+// ---------------------------------------------------------------------------
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+int max_cols_for(int D) { return D <= 32 ? 384 : (D <= 64 ? 320 : 160); }
+
+struct Plan {
+  FwdParams p;
+  size_t smem;
+  bool ok;
+  const char* why;
+};
+
+// Shared memory: [Q stages][K stages][V stages][bitmap][barriers + tmem slot]
+size_t smem_needed(const FwdParams& p) {
+  const size_t q = (size_t)p.q_stages * p.ndblk * kTileM * p.row_bytes;
+  const size_t kv = (size_t)p.kv_stages * 2 * p.ndblk * p.n_pad * p.row_bytes;
+  return 1024 /*alignment slack*/ + q + kv + (size_t)kMaxWords * 128 * 4 + 256;
+}
+
+Plan make_plan(const Geo& g, int dtype) {
+  Plan pl{};
+  pl.ok = false;
+  FwdParams& p = pl.p;
+  if (dtype != NATTEN_B200_BF16 && dtype != NATTEN_B200_F16) { pl.why = "dtype is not bf16/f16"; return pl; }
+  if (g.D != 32 && g.D != 64 && g.D != 128) { pl.why = "head_dim is not 32, 64 or 128"; return pl; }
+  if (g.n_extra != 0) { pl.why = "extra tokens"; return pl; }
+  if (g.extents != nullptr) { pl.why = "per-sample extents"; return pl; }
+  if (!(g.scale > 0.f)) { pl.why = "scale is not positive"; return pl; }
+  int ncls = 1;
+  for (int a = 0; a < 3; ++a) {
+    if (g.st[a] != 1) { pl.why = "stride > 1"; return pl; }
+    if (g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a] || g.qo[a] != 0 || g.ko[a] != 0) { pl.why = "sharded slab"; return pl; }
+    ncls *= g.dl[a];
+  }
+  if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
+  p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.rep = g.rep; p.D = g.D; p.rank = g.rank;
+  for (int a = 0; a < 3; ++a) { p.L[a] = g.ge[a]; p.K[a] = g.K[a]; p.dl[a] = g.dl[a]; p.ca[a] = g.ca[a]; }
+  p.hpt = (g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1);
+  p.P = kTileM / p.hpt;
+  p.dblk = g.D == 32 ? 32 : 64;
+  p.ndblk = g.D / p.dblk;
+  p.row_bytes = p.dblk * 2;
+  p.layout_type = g.D == 32 ? 4 : 2;
+  const int nmax = max_cols_for(g.D);
+
+  int lgmax[3];
+  for (int a = 0; a < 3; ++a) lgmax[a] = ceil_div(g.ge[a], g.dl[a]);
+  long long best_cost = -1;
+  for (int t2 = 1; t2 <= p.P; t2 *= 2)
+    for (int t1 = 1; t1 * t2 <= p.P; t1 *= 2) {
+      const int t0 = p.P / (t1 * t2);
+      const int T[3] = {t0, t1, t2};
+      bool skip = false;
+      int box[3];
+      for (int a = 0; a < 3; ++a) {
+        if (g.ge[a] == 1 && T[a] != 1) skip = true;          // nothing to tile on a trivial axis
+        const int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1;
+        box[a] = need < lgmax[a] ? need : lgmax[a];
+        if (box[a] > 256) skip = true;                        // TMA box limit
+      }
+      if (skip) continue;
+      int ca, R;
+      const long long v2 = box[2], v1 = (long long)box[1] * box[2], v0 = (long long)box[0] * v1;
+      if (v0 <= nmax) { ca = 0; R = box[0]; }
+      else if (v1 <= nmax) { ca = 0; R = (int)(nmax / v1); }
+      else if (v2 <= nmax) { ca = 1; R = (int)(nmax / v2); }
+      else continue;
+      const int inner = ca == 0 ? (int)v1 : (int)v2;
+      const int cch = ceil_div(box[ca], R);
+      R = ceil_div(box[ca], cch);                             // even out the chunks
+      const int nch = (ca == 1 ? box[0] : 1) * cch;
+      int n_pad = (R * inner + 15) & ~15;
+      if (n_pad > 256) n_pad = (n_pad + 31) & ~31;
+      if (n_pad > nmax) continue;
+      long long tiles = 1;
+      for (int a = 0; a < 3; ++a) tiles *= ceil_div(lgmax[a], T[a]);
+      const long long cost = tiles * nch * (n_pad + 64);      // +64: fixed per-chunk overhead
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(lgmax[a], T[a]); }
+        p.chunk_axis = ca; p.R = R; p.cchunks = cch; p.n_chunks = nch; p.inner = inner;
+        p.n_cols = R * inner; p.n_pad = n_pad;
+      }
+    }
+  if (best_cost < 0) { pl.why = "no tile shape fits the key box into tensor memory"; return pl; }
+  p.n_split = p.n_pad > 256 ? 2 : 1;
+  p.n_half = p.n_pad / p.n_split;
+  p.q_stages = 2; p.kv_stages = 2;
+  if (smem_needed(p) > 227 * 1024) p.q_stages = 1;
+  if (smem_needed(p) > 227 * 1024) p.kv_stages = 1;
+  if (smem_needed(p) > 227 * 1024) { pl.why = "shared memory"; return pl; }
+  pl.smem = smem_needed(p);
+  p.n_work = (long long)g.B * g.Hkv * (g.rep / p.hpt) * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
+  p.scale_log2 = g.scale * 1.4426950408889634f;
+  p.is_bf16 = dtype == NATTEN_B200_BF16;
+  const int fmt = p.is_bf16 ? 1 : 0;
+  p.idesc_qk = instr_desc(kTileM, p.n_half, fmt, 0, 0);
+  p.idesc_pv = instr_desc(kTileM, g.D, fmt, 0, 1);
+  pl.ok = true;
+  pl.why = "";
+  return pl;
+}
+
+// ---------------------------------------------------------------------------
+// host: tensor maps
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// One map per dilation class for a [B, spatial..., heads, D] tensor.
+// dims: (heads*D, axis rank-1, ..., axis 0, B); box_sp[a] is the box extent on
+// normalised axis a (leading trivial axes of lower-rank tensors are skipped).
+int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, int heads, const int box_sp[3]) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return set_error(NATTEN_B200_ENODEVICE, "cuTensorMapEncodeTiled is not available");
+  const int lead = 3 - p.rank;
+  const cuuint32_t trank = (cuuint32_t)(p.rank + 2);
+  long long stride_el[3];  // elements between consecutive coordinates on each axis
+  long long s = (long long)heads * p.D;
+  for (int a = 2; a >= 0; --a) { stride_el[a] = s; s *= p.L[a]; }
+  const long long batch_el = s;
+  int ci = 0;
+  for (int g0 = 0; g0 < p.dl[0]; ++g0)
+    for (int g1 = 0; g1 < p.dl[1]; ++g1)
+      for (int g2 = 0; g2 < p.dl[2]; ++g2, ++ci) {
+        const int gcls[3] = {g0, g1, g2};
+        cuuint64_t dims[5];
+        cuuint64_t strides[4];
+        cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+        long long off = 0;
+        dims[0] = (cuuint64_t)heads * p.D;
+        box[0] = (cuuint32_t)p.dblk;
+        int di = 1;
+        for (int a = 2; a >= lead; --a, ++di) {
+          dims[di] = (cuuint64_t)ceil_div(p.L[a] - gcls[a], p.dl[a]);
+          strides[di - 1] = (cuuint64_t)(stride_el[a] * p.dl[a] * 2);
+          box[di] = (cuuint32_t)box_sp[a];
+          off += gcls[a] * stride_el[a];
+        }
+        dims[di] = (cuuint64_t)p.B;
+        strides[di - 1] = (cuuint64_t)(batch_el * 2);
+        box[di] = 1;
+        void* ptr = const_cast<char*>(static_cast<const char*>(base)) + off * 2;
+        const CUresult r = enc(&maps[ci], p.is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                               trank, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               p.D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(NATTEN_B200_ELAUNCH, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+      }
+  return 0;
+}
+
+}  // namespace
 }  // namespace nb
+
+#include "fna_sm100_fwd_kernel.inc"

@@ -15,4 +15,12 @@ int run_fused_forward_sm100(const Geo& g, int dtype, const FusedArgs& a, cudaStr
 int run_fused_backward_sm100(const Geo& g, int dtype, const FusedArgs& a, cudaStream_t s);
 size_t fused_backward_scratch_sm100(const Geo& g, int dtype);
 
+// 1 when a tensor-core kernel on the current device gave up on a wait since
+// the last call (synchronises with the device and clears the flag).
+int sm100_read_status();
+// Diagnostic: when set, the forward dumps the raw S of its first tile here.
+void sm100_set_debug_s(float* ptr);
+// Text description of the tiling chosen for a geometry (no GPU needed).
+int sm100_describe_plan(const Geo& g, int dtype, char* buf, size_t cap);
+
 }  // namespace nb

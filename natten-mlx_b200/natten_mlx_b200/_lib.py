@@ -67,6 +67,9 @@ SYMBOLS = {
     "natten_b200_fused_forward": (ctypes.c_int, [_G] + [_P] * 8),
     "natten_b200_fused_backward_scratch_bytes": (ctypes.c_size_t, [_G]),
     "natten_b200_fused_backward": (ctypes.c_int, [_G] + [_P] * 15 + [ctypes.c_size_t, _P]),
+    "natten_b200_kernel_status": (ctypes.c_int, []),
+    "natten_b200_debug_set_s_dump": (None, [_P]),
+    "natten_b200_describe_plan": (ctypes.c_int, [_G, ctypes.c_char_p, ctypes.c_size_t]),
     "natten_b200_merge_forward": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32] + [_P] * 7),
     "natten_b200_merge_backward": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32] + [_P] * 11),
 }
@@ -124,6 +127,17 @@ def trace_report() -> dict:
         name, n, ms = line.split()
         out[name] = (int(n), float(ms))
     return out
+
+
+def kernel_status() -> int:
+    """1 if a tensor-core kernel gave up on a wait since the last call (synchronises)."""
+    return int(load().natten_b200_kernel_status())
+
+
+def describe_plan(geom: "Geom") -> str:
+    buf = ctypes.create_string_buffer(512)
+    check(load().natten_b200_describe_plan(geom, buf, len(buf)))
+    return buf.value.decode()
 
 
 def check(rc: int) -> None:

@@ -1,0 +1,75 @@
+"""The tensor-core (tcgen05 / TMEM / TMA) fused kernels against the CPU oracle
+and against the CUDA-core kernels, through the C ABI with the kernel family
+forced.  bf16 / fp16 tolerance: 2e-2 of the largest reference magnitude."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import natten_oracle as oracle
+
+from natten_mlx_b200 import _lib
+from natten_mlx_b200._core import cuda as backend
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(shape, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(shape, generator=g, dtype=torch.float32).to(dtype)
+
+
+def _rel(got, want):
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    fin = torch.isfinite(want)
+    assert torch.equal(torch.isfinite(got), fin)
+    return float((got[fin] - want[fin]).abs().max() / want[fin].abs().max().clamp_min(1e-6))
+
+
+CASES = [
+    # shape [B, spatial..., Hq, D], heads_kv, kernel, dilation, causal
+    ((1, 16, 8, 1, 32), 1, (3, 3), (1, 1), (False, False)),          # one tile, one chunk
+    ((2, 56, 56, 4, 32), 4, (7, 7), (1, 1), (False, False)),         # the NAT-stage shape
+    ((1, 56, 56, 2, 32), 2, (7, 7), (4, 4), (False, False)),         # 16 dilation classes
+    ((1, 30, 23, 2, 32), 2, (5, 7), (2, 3), (True, False)),          # ragged classes, causal axis
+    ((2, 150, 4, 32), 4, (7,), (1,), (False,)),                      # 1D
+    ((1, 300, 2, 64), 2, (31,), (2,), (True,)),                      # 1D causal, D=64
+    ((1, 20, 24, 2, 64), 2, (7, 7), (1, 2), (False, False)),         # D=64 (128-byte swizzle)
+    ((1, 18, 20, 2, 128), 2, (5, 5), (1, 1), (False, False)),        # D=128 (two 64-wide blocks)
+    ((1, 6, 16, 18, 2, 64), 2, (3, 7, 7), (1, 2, 2), (True, False, False)),   # 3D, several chunks
+    ((1, 5, 9, 12, 2, 32), 2, (3, 3, 5), (1, 1, 1), (False, False, False)),
+    ((1, 20, 22, 8, 128), 2, (13, 13), (1, 1), (False, False)),      # GQA: 4 query heads packed per tile
+    ((1, 12, 14, 4, 32), 2, (4, 6), (1, 1), (False, False)),         # even kernels
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,hkv,ks,dl,ca", CASES)
+def test_tcgen05_forward(dtype, shape, hkv, ks, dl, ca):
+    rank = len(shape) - 3
+    kv_shape = shape[:-2] + (hkv, shape[-1])
+    q, k, v = _rand(shape, 1, dtype), _rand(kv_shape, 2, dtype), _rand(kv_shape, 3, dtype)
+    one = (1,) * rank
+    o_ref, l_ref = oracle.na(q.float(), k.float(), v.float(), ks, 1, dl, ca, return_lse=True)
+    out, lse = backend.fused_forward(q.to(DEV), k.to(DEV), v.to(DEV), ks, one, dl, ca, None, path="tcgen05")
+    torch.cuda.synchronize()
+    assert _lib.last_path() == "tcgen05"
+    assert _lib.kernel_status() == 0, "a tensor-core kernel gave up on a wait"
+    assert out.dtype == dtype and lse.dtype == torch.float32
+    assert _rel(out, o_ref) < 2e-2
+    assert _rel(lse, l_ref) < 2e-2
+    # and against the CUDA-core kernels on the same inputs
+    out_s, lse_s = backend.fused_forward(q.to(DEV), k.to(DEV), v.to(DEV), ks, one, dl, ca, None, path="simt")
+    assert _rel(out, out_s) < 2e-2
+    assert _rel(lse, lse_s) < 5e-3
+
+
+def test_tcgen05_is_refused_for_unsupported_shapes():
+    q = torch.randn(1, 16, 2, 12, device=DEV)
+    with pytest.raises(ValueError, match="tcgen05"):
+        backend.fused_forward(q, q, q, (3,), (1,), (1,), (False,), None, path="tcgen05")
+    q = torch.randn(1, 16, 2, 32, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="stride"):
+        backend.fused_forward(q, q, q, (3,), (2,), (1,), (False,), None, path="tcgen05")
