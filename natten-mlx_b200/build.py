@@ -31,7 +31,8 @@ def _newest(paths):
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
-    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
+    headers = (glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(CSRC, "*.inc")) +
+               glob.glob(os.path.join(HERE, "..", "include", "*.h")))
     dep_time = _newest(headers) if headers else 0.0
 
     def compile_one(src):

@@ -18,6 +18,7 @@
 #include <cuda.h>
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -31,8 +32,7 @@ using namespace sm100;
 
 constexpr int kMaxClasses = 16;
 constexpr int kTileM = 128;
-constexpr int kMaxCols = 384;            // S columns per chunk (TMEM: S at 0, O at 384)
-constexpr int kOCol = 384;
+constexpr int kMaxCols = 384;            // S columns per chunk
 constexpr int kMaxGroups = kMaxCols / 16;
 constexpr int kMaxWords = kMaxCols / 32;
 constexpr int kThreads = 192;            // 4 softmax warps, 1 TMA warp, 1 MMA warp
@@ -50,9 +50,11 @@ struct FwdParams {
   int T[3];              // query tile extents in class coordinates
   int hpt, P;            // heads per tile, positions per tile (hpt * P == 128)
   int box[3];            // key box extents
+  int rp;                // 16 or 32: box rows padded to that many columns (box[2] == rp); 0: no row structure
   int chunk_axis, R, cchunks, n_chunks, inner, n_cols, n_pad, n_split, n_half;
   int dblk, ndblk, row_bytes, layout_type;
   int q_stages, kv_stages;
+  int ctas_per_sm, tmem_cols, ocol;   // TMEM: S/P at column 0, O at ocol
   int tiles[3];
   long long n_work;
   float scale_log2;
@@ -61,6 +63,7 @@ struct FwdParams {
   void* out;
   float* lse;
   int* status;
+  unsigned long long* prof;  // optional cycle counters of CTA 0 (diagnostic)
   float* dbg_s;          // optional [n_chunks of the first work item][128][n_pad] raw S dump
 };
 
@@ -68,8 +71,6 @@ struct FwdParams {
 // host: planning
 // ---------------------------------------------------------------------------
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
-
-int max_cols_for(int D) { return D <= 32 ? 384 : (D <= 64 ? 320 : 160); }
 
 struct Plan {
   FwdParams p;
@@ -82,35 +83,12 @@ struct Plan {
 size_t smem_needed(const FwdParams& p) {
   const size_t q = (size_t)p.q_stages * p.ndblk * kTileM * p.row_bytes;
   const size_t kv = (size_t)p.kv_stages * 2 * p.ndblk * p.n_pad * p.row_bytes;
-  return 1024 /*alignment slack*/ + q + kv + (size_t)kMaxWords * 128 * 4 + 256;
+  return 1024 /*alignment slack*/ + q + kv + (size_t)kMaxWords * 128 * 4 + 512;
 }
 
-Plan make_plan(const Geo& g, int dtype) {
-  Plan pl{};
-  pl.ok = false;
-  FwdParams& p = pl.p;
-  if (dtype != NATTEN_B200_BF16 && dtype != NATTEN_B200_F16) { pl.why = "dtype is not bf16/f16"; return pl; }
-  if (g.D != 32 && g.D != 64 && g.D != 128) { pl.why = "head_dim is not 32, 64 or 128"; return pl; }
-  if (g.n_extra != 0) { pl.why = "extra tokens"; return pl; }
-  if (g.extents != nullptr) { pl.why = "per-sample extents"; return pl; }
-  if (!(g.scale > 0.f)) { pl.why = "scale is not positive"; return pl; }
-  int ncls = 1;
-  for (int a = 0; a < 3; ++a) {
-    if (g.st[a] != 1) { pl.why = "stride > 1"; return pl; }
-    if (g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a] || g.qo[a] != 0 || g.ko[a] != 0) { pl.why = "sharded slab"; return pl; }
-    ncls *= g.dl[a];
-  }
-  if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
-  p.B = g.B; p.Hq = g.Hq; p.Hkv = g.Hkv; p.rep = g.rep; p.D = g.D; p.rank = g.rank;
-  for (int a = 0; a < 3; ++a) { p.L[a] = g.ge[a]; p.K[a] = g.K[a]; p.dl[a] = g.dl[a]; p.ca[a] = g.ca[a]; }
-  p.hpt = (g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1);
-  p.P = kTileM / p.hpt;
-  p.dblk = g.D == 32 ? 32 : 64;
-  p.ndblk = g.D / p.dblk;
-  p.row_bytes = p.dblk * 2;
-  p.layout_type = g.D == 32 ? 4 : 2;
-  const int nmax = max_cols_for(g.D);
-
+// Best query tile for a cap of `nmax` S columns per chunk; returns the cost
+// (tiles x chunks x padded columns) or -1 when nothing fits.
+long long choose_tile(const Geo& g, FwdParams& p, int nmax) {
   int lgmax[3];
   for (int a = 0; a < 3; ++a) lgmax[a] = ceil_div(g.ge[a], g.dl[a]);
   long long best_cost = -1;
@@ -127,6 +105,10 @@ Plan make_plan(const Geo& g, int dtype) {
         if (box[a] > 256) skip = true;                        // TMA box limit
       }
       if (skip) continue;
+      // box rows of at most 32 keys are padded to 16 or 32 columns, so that a
+      // 16-column group of S never straddles two box rows
+      const int rp = box[2] <= 16 ? 16 : (box[2] <= 32 ? 32 : 0);
+      if (rp != 0) box[2] = rp;
       int ca, R;
       const long long v2 = box[2], v1 = (long long)box[1] * box[2], v0 = (long long)box[0] * v1;
       if (v0 <= nmax) { ca = 0; R = box[0]; }
@@ -142,23 +124,77 @@ Plan make_plan(const Geo& g, int dtype) {
       if (n_pad > nmax) continue;
       long long tiles = 1;
       for (int a = 0; a < 3; ++a) tiles *= ceil_div(lgmax[a], T[a]);
-      const long long cost = tiles * nch * (n_pad + 64);      // +64: fixed per-chunk overhead
+      const long long cost = tiles * nch * (n_pad + 96);      // +96: fixed per-chunk overhead
       if (best_cost < 0 || cost < best_cost) {
         best_cost = cost;
         for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(lgmax[a], T[a]); }
         p.chunk_axis = ca; p.R = R; p.cchunks = cch; p.n_chunks = nch; p.inner = inner;
-        p.n_cols = R * inner; p.n_pad = n_pad;
+        p.n_cols = R * inner; p.n_pad = n_pad; p.rp = rp;
       }
     }
-  if (best_cost < 0) { pl.why = "no tile shape fits the key box into tensor memory"; return pl; }
+  return best_cost;
+}
+
+Plan make_plan(const Geo& g, int dtype) {
+  Plan pl{};
+  pl.ok = false;
+  FwdParams base{};
+  if (dtype != NATTEN_B200_BF16 && dtype != NATTEN_B200_F16) { pl.why = "dtype is not bf16/f16"; return pl; }
+  if (g.D != 32 && g.D != 64 && g.D != 128) { pl.why = "head_dim is not 32, 64 or 128"; return pl; }
+  if (g.n_extra != 0) { pl.why = "extra tokens"; return pl; }
+  if (g.extents != nullptr) { pl.why = "per-sample extents"; return pl; }
+  if (!(g.scale > 0.f)) { pl.why = "scale is not positive"; return pl; }
+  int ncls = 1;
+  for (int a = 0; a < 3; ++a) {
+    if (g.st[a] != 1) { pl.why = "stride > 1"; return pl; }
+    if (g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a] || g.qo[a] != 0 || g.ko[a] != 0) { pl.why = "sharded slab"; return pl; }
+    ncls *= g.dl[a];
+  }
+  if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
+  base.B = g.B; base.Hq = g.Hq; base.Hkv = g.Hkv; base.rep = g.rep; base.D = g.D; base.rank = g.rank;
+  for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
+  base.hpt = (g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1);
+  base.P = kTileM / base.hpt;
+  base.dblk = g.D == 32 ? 32 : 64;
+  base.ndblk = g.D / base.dblk;
+  base.row_bytes = base.dblk * 2;
+  base.layout_type = g.D == 32 ? 4 : 2;
+
+  // Two CTAs per SM (256 TMEM columns and half the shared memory each) let one
+  // CTA's MMA/TMA phases run under the other's softmax; one CTA per SM allows
+  // larger chunks.  Every feasible (CTAs, column cap) pair is costed.
+  double best = -1.0;
+  static const int caps[] = {384, 320, 256, 224, 192, 160, 128, 96, 64};
+  const char* force = getenv("NATTEN_B200_CTAS_PER_SM");   // tuning aid: pin the CTAs per SM
+  const int forced = force != nullptr ? atoi(force) : 0;
+  for (int ctas = 2; ctas >= 1; --ctas) {
+    if (forced >= 1 && forced <= 2 && ctas != forced) continue;
+    const int tmem_cols = 512 / ctas;
+    const size_t smem_limit = ctas == 2 ? 113 * 1024 : 227 * 1024;
+    for (int cap : caps) {
+      if (cap > tmem_cols - g.D || cap > kMaxCols) continue;
+      FwdParams p = base;
+      const long long cost = choose_tile(g, p, cap);
+      if (cost < 0) continue;
+      p.q_stages = 2; p.kv_stages = 2;
+      if (smem_needed(p) > smem_limit) p.q_stages = 1;
+      if (smem_needed(p) > smem_limit) continue;           // a single K/V stage would lose the prefetch
+      const double eff = (double)cost / (ctas == 2 ? 1.7 : 1.0);
+      if (best < 0 || eff < best) {
+        best = eff;
+        p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - g.D;
+        pl.p = p;
+      }
+    }
+  }
+  if (best < 0) { pl.why = "no tile shape fits the key box into tensor and shared memory"; return pl; }
+  FwdParams& p = pl.p;
   p.n_split = p.n_pad > 256 ? 2 : 1;
   p.n_half = p.n_pad / p.n_split;
-  p.q_stages = 2; p.kv_stages = 2;
-  if (smem_needed(p) > 227 * 1024) p.q_stages = 1;
-  if (smem_needed(p) > 227 * 1024) p.kv_stages = 1;
-  if (smem_needed(p) > 227 * 1024) { pl.why = "shared memory"; return pl; }
   pl.smem = smem_needed(p);
-  p.n_work = (long long)g.B * g.Hkv * (g.rep / p.hpt) * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
+  const long long n_work = (long long)g.B * g.Hkv * (g.rep / p.hpt) * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
+  if (n_work >= (1LL << 31)) { pl.why = "more than 2^31 tiles"; return pl; }
+  p.n_work = n_work;
   p.scale_log2 = g.scale * 1.4426950408889634f;
   p.is_bf16 = dtype == NATTEN_B200_BF16;
   const int fmt = p.is_bf16 ? 1 : 0;

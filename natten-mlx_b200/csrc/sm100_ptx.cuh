@@ -38,19 +38,23 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// A waiting thread is suspended by the hardware until the phase completes or
+// the hint (in nanoseconds) runs out, so waiting warps do not take issue slots
+// from the warps that compute.
+constexpr uint32_t kSuspendHintNs = 1000000u;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred P1;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2, %3;\n\t"
       "selp.b32 %0, 1, 0, P1;\n\t}\n"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
 
-constexpr uint32_t kSpinLimit = 1u << 22;  // try_wait calls before a wait gives up
+constexpr uint32_t kSpinLimit = 4000;  // try_wait calls (about 1 ms each at most) before a wait gives up
 
 // Waits for the phase with the given parity.  Returns false when the CTA is
 // aborting (this wait ran out, or another one did before).
