@@ -331,7 +331,11 @@ int natten_b200_describe_plan(const natten_b200_geom* gi, char* buf, size_t cap)
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;
   if (buf == nullptr || cap == 0) return set_error(NATTEN_B200_EINVAL, "describe_plan: null buffer");
-  sm100_describe_plan(g, gi->dtype, buf, cap);
+  int n = sm100_describe_plan(g, gi->dtype, 0, buf, cap);
+  for (int mode = 1; mode <= 2 && n > 0 && (size_t)n + 8 < cap; ++mode) {
+    n += snprintf(buf + n, cap - n, mode == 1 ? " | dQ: " : " | dK/dV: ");
+    n += sm100_describe_plan(g, gi->dtype, mode, buf + n, cap - n);
+  }
   return NATTEN_B200_OK;
 }
 

@@ -43,6 +43,15 @@ struct alignas(64) TmaMaps {
   CUtensorMap v[kMaxClasses];
 };
 
+// Backward: r1/r2 are the row operands of a tile (Q, dO | K, V), c1/c2 the
+// chunk operands (K, V | Q, dO).
+struct alignas(64) TmaMapsBwd {
+  CUtensorMap r1[kMaxClasses];
+  CUtensorMap r2[kMaxClasses];
+  CUtensorMap c1[kMaxClasses];
+  CUtensorMap c2[kMaxClasses];
+};
+
 struct FwdParams {
   int B, Hq, Hkv, rep, D;
   int rank;              // spatial rank of the tensors (tensor-map rank = rank + 2)
@@ -55,6 +64,12 @@ struct FwdParams {
   int dblk, ndblk, row_bytes, layout_type;
   int q_stages, kv_stages;
   int ctas_per_sm, tmem_cols, ocol;   // TMEM: S/P at column 0, O at ocol
+  // backward kernels: mode 1 = dQ (rows are queries), mode 2 = dK/dV (rows are keys)
+  int mode, head_groups;
+  int dp_col, acc_col, acc2_col;      // TMEM: dP at dp_col, dQ | dK at acc_col, dV at acc2_col
+  const float* lse_in;                // saved log-sum-exp [rows of out] (natural log)
+  const float* delta;                 // rowsum(dO * O) - dLSE [rows of out]
+  void* out2;                         // dV (mode 2)
   int tiles[3];
   long long n_work;
   float scale_log2;
@@ -81,14 +96,16 @@ struct Plan {
 
 // Shared memory: [Q stages][K stages][V stages][bitmap][barriers + tmem slot]
 size_t smem_needed(const FwdParams& p) {
-  const size_t q = (size_t)p.q_stages * p.ndblk * kTileM * p.row_bytes;
+  const size_t row_tiles = p.mode == 0 ? 1 : 2;   // forward: Q; backward: two row operands
+  const size_t q = (size_t)p.q_stages * row_tiles * p.ndblk * kTileM * p.row_bytes;
   const size_t kv = (size_t)p.kv_stages * 2 * p.ndblk * p.n_pad * p.row_bytes;
-  return 1024 /*alignment slack*/ + q + kv + (size_t)kMaxWords * 128 * 4 + 512;
+  const size_t stats = p.mode == 2 ? (size_t)p.kv_stages * 2 * p.n_pad * 4 : 0;   // per-column lse / delta
+  return 1024 /*alignment slack*/ + q + kv + stats + (size_t)kMaxWords * 128 * 4 + 512;
 }
 
 // Best query tile for a cap of `nmax` S columns per chunk; returns the cost
 // (tiles x chunks x padded columns) or -1 when nothing fits.
-long long choose_tile(const Geo& g, FwdParams& p, int nmax) {
+long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
   int lgmax[3];
   for (int a = 0; a < 3; ++a) lgmax[a] = ceil_div(g.ge[a], g.dl[a]);
   long long best_cost = -1;
@@ -100,7 +117,9 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax) {
       int box[3];
       for (int a = 0; a < 3; ++a) {
         if (g.ge[a] == 1 && T[a] != 1) skip = true;          // nothing to tile on a trivial axis
-        const int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1;
+        // keys a query tile addresses: T + K - 1; queries that address a key tile: one more at
+        // most, because windows pulled inward at an edge also cover keys further in
+        const int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1 + ((mode == 2 && g.ca[a] == 0) ? 1 : 0);
         box[a] = need < lgmax[a] ? need : lgmax[a];
         if (box[a] > 256) skip = true;                        // TMA box limit
       }
@@ -135,7 +154,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax) {
   return best_cost;
 }
 
-Plan make_plan(const Geo& g, int dtype) {
+Plan make_plan(const Geo& g, int dtype, int mode = 0) {
   Plan pl{};
   pl.ok = false;
   FwdParams base{};
@@ -153,7 +172,9 @@ Plan make_plan(const Geo& g, int dtype) {
   if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
   base.B = g.B; base.Hq = g.Hq; base.Hkv = g.Hkv; base.rep = g.rep; base.D = g.D; base.rank = g.rank;
   for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
-  base.hpt = (g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1);
+  base.mode = mode;
+  base.hpt = mode == 2 ? 1 : ((g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1));
+  base.head_groups = mode == 2 ? 1 : g.rep / base.hpt;
   base.P = kTileM / base.hpt;
   base.dblk = g.D == 32 ? 32 : 64;
   base.ndblk = g.D / base.dblk;
@@ -172,9 +193,11 @@ Plan make_plan(const Geo& g, int dtype) {
     const int tmem_cols = 512 / ctas;
     const size_t smem_limit = ctas == 2 ? 113 * 1024 : 227 * 1024;
     for (int cap : caps) {
-      if (cap > tmem_cols - g.D || cap > kMaxCols) continue;
+      const int acc_cols = mode == 2 ? 2 * g.D : g.D;
+      const int s_regions = mode == 0 ? 1 : 2;
+      if (cap * s_regions > tmem_cols - acc_cols || cap > kMaxCols) continue;
       FwdParams p = base;
-      const long long cost = choose_tile(g, p, cap);
+      const long long cost = choose_tile(g, p, cap, mode);
       if (cost < 0) continue;
       p.q_stages = 2; p.kv_stages = 2;
       if (smem_needed(p) > smem_limit) p.q_stages = 1;
@@ -183,6 +206,7 @@ Plan make_plan(const Geo& g, int dtype) {
       if (best < 0 || eff < best) {
         best = eff;
         p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - g.D;
+        p.dp_col = p.n_pad; p.acc_col = tmem_cols - acc_cols; p.acc2_col = tmem_cols - g.D;
         pl.p = p;
       }
     }
@@ -192,7 +216,7 @@ Plan make_plan(const Geo& g, int dtype) {
   p.n_split = p.n_pad > 256 ? 2 : 1;
   p.n_half = p.n_pad / p.n_split;
   pl.smem = smem_needed(p);
-  const long long n_work = (long long)g.B * g.Hkv * (g.rep / p.hpt) * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
+  const long long n_work = (long long)g.B * g.Hkv * p.head_groups * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
   if (n_work >= (1LL << 31)) { pl.why = "more than 2^31 tiles"; return pl; }
   p.n_work = n_work;
   p.scale_log2 = g.scale * 1.4426950408889634f;
@@ -274,3 +298,5 @@ int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, i
 }  // namespace nb
 
 #include "fna_sm100_fwd_kernel.inc"
+#include "fna_sm100_bwd_kernel.inc"
+#include "fna_sm100_host.inc"

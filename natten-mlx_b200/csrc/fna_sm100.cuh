@@ -21,6 +21,7 @@ int sm100_read_status();
 // Diagnostic: when set, the forward dumps the raw S of its first tile here.
 void sm100_set_debug_s(float* ptr);
 // Text description of the tiling chosen for a geometry (no GPU needed).
-int sm100_describe_plan(const Geo& g, int dtype, char* buf, size_t cap);
+// mode: 0 forward, 1 dQ kernel, 2 dK/dV kernel.
+int sm100_describe_plan(const Geo& g, int dtype, int mode, char* buf, size_t cap);
 
 }  // namespace nb

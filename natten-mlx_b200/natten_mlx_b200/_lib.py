@@ -135,7 +135,7 @@ def kernel_status() -> int:
 
 
 def describe_plan(geom: "Geom") -> str:
-    buf = ctypes.create_string_buffer(512)
+    buf = ctypes.create_string_buffer(2048)
     check(load().natten_b200_describe_plan(geom, buf, len(buf)))
     return buf.value.decode()
 

@@ -73,3 +73,29 @@ def test_tcgen05_is_refused_for_unsupported_shapes():
     q = torch.randn(1, 16, 2, 32, device=DEV, dtype=torch.bfloat16)
     with pytest.raises(ValueError, match="stride"):
         backend.fused_forward(q, q, q, (3,), (2,), (1,), (False,), None, path="tcgen05")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,hkv,ks,dl,ca", CASES)
+def test_tcgen05_backward(dtype, shape, hkv, ks, dl, ca):
+    rank = len(shape) - 3
+    kv_shape = shape[:-2] + (hkv, shape[-1])
+    q, k, v = _rand(shape, 1, dtype), _rand(kv_shape, 2, dtype), _rand(kv_shape, 3, dtype)
+    cot, cot_l = _rand(shape, 4, dtype), _rand(shape[:-1], 5, torch.float32)
+    one = (1,) * rank
+    fn = lambda a, b, c: oracle.na(a, b, c, ks, 1, dl, ca, return_lse=True)
+    _, g_ref = oracle.grads(fn, [q.float(), k.float(), v.float()], (cot.float(), cot_l))
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out, lse = backend.fused_forward(qd, kd, vd, ks, one, dl, ca, None, path="tcgen05")
+    dq, dk, dv, _, _ = backend.fused_backward(qd, kd, vd, out, lse, cot.to(DEV), cot_l.to(DEV), ks, one, dl, ca, None,
+                                              path="tcgen05")
+    torch.cuda.synchronize()
+    assert _lib.last_path() == "tcgen05"
+    assert _lib.kernel_status() == 0, "a tensor-core kernel gave up on a wait"
+    for name, got, want in zip(("dq", "dk", "dv"), (dq, dk, dv), g_ref):
+        assert got.dtype == dtype
+        assert _rel(got, want) < 2e-2, name
+    # bit-identical on a second run (no atomics anywhere)
+    dq2, dk2, dv2, _, _ = backend.fused_backward(qd, kd, vd, out, lse, cot.to(DEV), cot_l.to(DEV), ks, one, dl, ca,
+                                                 None, path="tcgen05")
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
