@@ -215,6 +215,31 @@ int natten_b200_fused_backward(const natten_b200_geom* g, const void* q, const v
                                size_t scratch_bytes, void* stream);
 
 /*
+ * The fused backward for callers that cannot allocate device memory where the
+ * backward runs (an allocator frozen while an execution plan is recorded or
+ * replayed, a fixed-budget serving loop, a sandbox that only hands out
+ * pre-registered buffers).  Same arguments and results as
+ * natten_b200_fused_backward, minus the scratch buffer: the scratch lives in a
+ * fixed array inside the library image (natten_b200_static_scratch_capacity()
+ * bytes, 4 MiB, held by every GPU that loads the library until the process
+ * exits).  A geometry whose natten_b200_fused_backward_scratch_bytes() exceeds
+ * the capacity is refused with NATTEN_B200_ERESOURCE.  The call allocates
+ * nothing: no cudaMalloc / cudaFree and no allocating library routine.
+ * The first call on a device looks the array's device address up (with that
+ * device current); make that first call before any stream capture.
+ * All calls share the one array, whose contents are whatever the last call
+ * left; the kernels rewrite or clear what they read, but two calls that overlap
+ * on the GPU (different streams) race on it.
+ * This entry point has no counterpart in the reference.
+ */
+size_t natten_b200_static_scratch_capacity(void);
+int natten_b200_fused_backward_static_scratch(const natten_b200_geom* g, const void* q, const void* k,
+                                              const void* v, const void* k_extra, const void* v_extra,
+                                              const void* out, const float* lse, const void* dout,
+                                              const float* dlse, void* dq, void* dk, void* dv,
+                                              void* dk_extra, void* dv_extra, void* stream);
+
+/*
  * Merge two attention results over the same queries:
  * out = o0 - sigmoid(l1 - l0) * (o0 - o1), lse = l0 - logsigmoid(l0 - l1).
  * rows = number of (query, head) rows, o* are [rows, head_dim] in dtype,

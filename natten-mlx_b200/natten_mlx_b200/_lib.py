@@ -67,6 +67,8 @@ SYMBOLS = {
     "natten_b200_fused_forward": (ctypes.c_int, [_G] + [_P] * 8),
     "natten_b200_fused_backward_scratch_bytes": (ctypes.c_size_t, [_G]),
     "natten_b200_fused_backward": (ctypes.c_int, [_G] + [_P] * 15 + [ctypes.c_size_t, _P]),
+    "natten_b200_static_scratch_capacity": (ctypes.c_size_t, []),
+    "natten_b200_fused_backward_static_scratch": (ctypes.c_int, [_G] + [_P] * 15),
     "natten_b200_kernel_status": (ctypes.c_int, []),
     "natten_b200_debug_set_s_dump": (None, [_P]),
     "natten_b200_describe_plan": (ctypes.c_int, [_G, ctypes.c_char_p, ctypes.c_size_t]),
