@@ -185,13 +185,16 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
   // CTA's MMA/TMA phases run under the other's softmax; one CTA per SM allows
   // larger chunks.  Every feasible (CTAs, column cap) pair is costed.
   double best = -1.0;
-  static const int caps[] = {384, 320, 256, 224, 192, 160, 128, 96, 64};
+  static const int caps[] = {384, 320, 256, 224, 192, 160, 128, 96, 64, 48, 32};
   const char* force = getenv("NATTEN_B200_CTAS_PER_SM");   // tuning aid: pin the CTAs per SM
   const int forced = force != nullptr ? atoi(force) : 0;
-  for (int ctas = 2; ctas >= 1; --ctas) {
-    if (forced >= 1 && forced <= 2 && ctas != forced) continue;
-    const int tmem_cols = 512 / ctas;
-    const size_t smem_limit = ctas == 2 ? 113 * 1024 : 227 * 1024;
+  // registers per thread of the kernels cap the CTAs per SM: forward 2, dQ 4, dK/dV 2
+  const int max_ctas = mode == 1 ? 4 : 2;
+  static const double overlap[5] = {0.0, 1.0, 1.7, 2.3, 2.8};
+  for (int ctas = max_ctas; ctas >= 1; --ctas) {
+    if (forced >= 1 && forced <= 4 && ctas != (forced < max_ctas ? forced : max_ctas)) continue;
+    const int tmem_cols = ctas >= 3 ? 128 : 512 / ctas;   // a power of two per CTA
+    const size_t smem_limit = (size_t)(232448 / ctas) - 1024;
     for (int cap : caps) {
       const int acc_cols = mode == 2 ? 2 * g.D : g.D;
       const int s_regions = mode == 0 ? 1 : 2;
@@ -202,7 +205,7 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
       p.q_stages = 2; p.kv_stages = 2;
       if (smem_needed(p) > smem_limit) p.q_stages = 1;
       if (smem_needed(p) > smem_limit) continue;           // a single K/V stage would lose the prefetch
-      const double eff = (double)cost / (ctas == 2 ? 1.7 : 1.0);
+      const double eff = (double)cost / overlap[ctas];
       if (best < 0 || eff < best) {
         best = eff;
         p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - g.D;
