@@ -51,7 +51,7 @@ WORKLOADS = {
                            causal=(False, False), dtype="bf16",
                            label="na2d bf16 B=32 56x56 H=4 D=32 K=7x7 dilation {1,4} fwd+bwd"),
     "na3d_video": dict(shape=(2, 32, 96, 96, 16, 64), heads_kv=16, kernel=(3, 7, 7), dilations=[(1, 2, 2)],
-                       causal=(True, False, False), dtype="bf16",
+                       causal=(True, False, False), dtype="bf16", cpu_shape=(1, 4, 32, 32, 2, 64),
                        label="na3d bf16 B=2 T=32 96x96 H=16 D=64 K=(3,7,7) causal-T dilation (1,2,2) fwd+bwd"),
     "na1d_parity": dict(shape=(2, 64, 4, 32), heads_kv=4, kernel=(7,), dilations=[(1,)], causal=(False,),
                         dtype="f32", label="na1d fp32 B=2 L=64 H=4 D=32 K=7 fwd+bwd"),
@@ -102,6 +102,12 @@ def algorithmic_bytes(w):
     return {"fused_fwd": fwd, "fused_bwd_q": bwd_q, "fused_bwd_kv": bwd_kv,
             "fna_fwd_sm100": fwd, "fna_bwd_dq_sm100": bwd_q, "fna_bwd_dkv_sm100": bwd_kv,
             "fna_bwd_prep_sm100": 2 * tq + 2 * tl}
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of one forward+backward call of
+# the default workload; workloads without a capture report null.
+NCU_TRAFFIC = {"na2d_nat_stage": {"fna_fwd_sm100": 86.1e6, "fna_bwd_dq_sm100": 118.6e6, "fna_bwd_dkv_sm100": 129.4e6,
+                                  "fna_bwd_prep_sm100": 51.5e6}}
 
 
 def make_inputs(w, seed, device, pinned=False):
@@ -171,10 +177,17 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # the reference arm / CPU baseline: the oracle on the host cores
 # ---------------------------------------------------------------------------
+def cpu_sample_workload(w, batch):
+    """The bounded sample the CPU legs run: `batch` samples, or the workload's reduced `cpu_shape`."""
+    if "cpu_shape" in w:
+        return dict(w, shape=tuple(w["cpu_shape"]), heads_kv=min(w["heads_kv"], w["cpu_shape"][-2]))
+    return dict(w, shape=(batch,) + tuple(w["shape"][1:]))
+
+
 def cpu_sample_step(w, batch):
-    """Forward + backward of every variant on `batch` samples with the CPU oracle (float32)."""
+    """Forward + backward of every variant on the bounded sample with the CPU oracle (float32)."""
     import natten_oracle as oracle
-    wb = dict(w, shape=(batch,) + tuple(w["shape"][1:]))
+    wb = cpu_sample_workload(w, batch)
     total = 0.0
     for vi, dil in enumerate(w["dilations"]):
         q, k, v, cot = (t.float() for t in make_inputs(wb, 1234 + vi, "cpu"))
@@ -199,8 +212,8 @@ def run_reference(args, w, rank, world):
         cpu_sample_step(w, batch)
     t = sum(cpu_sample_step(w, batch) for _ in range(args.steps))
     ms = t / args.steps * 1e3
-    tflops = flops_step(w) * batch / w["shape"][0] / (ms * 1e-3) / 1e12
-    sample = f"{batch} of {w['shape'][0]} samples per step, float32, both passes, every variant"
+    tflops = flops_step(cpu_sample_workload(w, batch)) / (ms * 1e-3) / 1e12
+    sample = f"shape {cpu_sample_workload(w, batch)['shape']} of {w['shape']} per step, float32, both passes, every variant"
     line = {
         "impl": "reference", "metric": "na_fwd_bwd_effective_tflops", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -326,7 +339,8 @@ def run_ours(args, w, rank, world, local_rank):
         if name in alg:
             achieved = alg[name] / (per_launch_ms * 1e-3) / 1e9
             roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                        "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                        "frac": achieved / hbm_peak, "traffic": NCU_TRAFFIC.get(args.workload, {}).get(name),
+                        "peak_kind": peak_kind,
                         "launch_ms": per_launch_ms, "share_of_device_time": share,
                         "algorithmic_bytes_per_launch": alg[name]}
     kernels = {k: {"launches": n, "ms_per_launch": ms / n} for k, (n, ms) in sorted(trace.items())}
@@ -340,10 +354,10 @@ def run_ours(args, w, rank, world, local_rank):
         while t_cpu < 10.0 and reps < 20:
             t_cpu += cpu_sample_step(w, batch)
             reps += 1
-        cpu_tflops = flops_step(w) * batch / w["shape"][0] * reps / t_cpu / 1e12
+        cpu_tflops = flops_step(cpu_sample_workload(w, batch)) * reps / t_cpu / 1e12
         cpu = {"value": cpu_tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-               "sample": f"{batch} of {w['shape'][0]} samples, {reps} repetitions, float32 CPU restatement of the "
-                         "reference's pure backend, forward+backward of every variant"}
+               "sample": f"shape {cpu_sample_workload(w, batch)['shape']} of {w['shape']}, {reps} repetitions, float32 "
+                         "CPU restatement of the reference's pure backend, forward+backward of every variant"}
 
     line = {
         "metric": "na_fwd_bwd_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
