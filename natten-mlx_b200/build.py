@@ -21,7 +21,7 @@ OBJ = os.path.join(HERE, "build")
 OUT = os.path.join(HERE, "natten_mlx_b200", "libnatten_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+         "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"] + os.environ.get("NATTEN_B200_NVCC_FLAGS", "").split()
 
 
 def _newest(paths):

@@ -196,19 +196,21 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
     const int tmem_cols = ctas >= 3 ? 128 : 512 / ctas;   // a power of two per CTA
     const size_t smem_limit = (size_t)(232448 / ctas) - 1024;
     for (int cap : caps) {
-      const int acc_cols = mode == 2 ? 2 * g.D : g.D;
-      const int s_regions = mode == 0 ? 1 : 2;
+      // forward: S/P and O double-buffered; backward: S and dP regions, single-buffered accumulators
+      const int acc_cols = mode == 1 ? g.D : 2 * g.D;
+      const int s_regions = 2;
       if (cap * s_regions > tmem_cols - acc_cols || cap > kMaxCols) continue;
       FwdParams p = base;
       const long long cost = choose_tile(g, p, cap, mode);
       if (cost < 0) continue;
-      p.q_stages = 2; p.kv_stages = 2;
+      p.q_stages = 2; p.kv_stages = mode == 0 ? 3 : 2;
+      if (smem_needed(p) > smem_limit) p.kv_stages = 2;
       if (smem_needed(p) > smem_limit) p.q_stages = 1;
       if (smem_needed(p) > smem_limit) continue;           // a single K/V stage would lose the prefetch
       const double eff = (double)cost / overlap[ctas];
       if (best < 0 || eff < best) {
         best = eff;
-        p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - g.D;
+        p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - 2 * g.D;
         p.dp_col = p.n_pad; p.acc_col = tmem_cols - acc_cols; p.acc2_col = tmem_cols - g.D;
         pl.p = p;
       }
