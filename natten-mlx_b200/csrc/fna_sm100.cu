@@ -63,6 +63,7 @@ struct FwdParams {
   int chunk_axis, R, cchunks, n_chunks, inner, n_cols, n_pad, n_split, n_half;
   int dblk, ndblk, row_bytes, layout_type;
   int q_stages, kv_stages;
+  int n_sbuf;                         // forward: depth of the S/P ring in tensor memory
   int ctas_per_sm, tmem_cols, ocol;   // TMEM: S/P at column 0, O at ocol
   // backward kernels: mode 1 = dQ (rows are queries), mode 2 = dK/dV (rows are keys)
   int mode, head_groups;
@@ -188,6 +189,10 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
   static const int caps[] = {384, 320, 256, 224, 192, 160, 128, 96, 64, 48, 32};
   const char* force = getenv("NATTEN_B200_CTAS_PER_SM");   // tuning aid: pin the CTAs per SM
   const int forced = force != nullptr ? atoi(force) : 0;
+  const char* env_cols = getenv("NATTEN_B200_MAX_COLS");   // tuning aids: cap the chunk width / ring depth
+  const int max_cols = env_cols != nullptr ? atoi(env_cols) : 0;
+  const char* env_sbuf = getenv("NATTEN_B200_MAX_SBUF");
+  const int max_sbuf = env_sbuf != nullptr ? atoi(env_sbuf) : 0;
   // registers per thread of the kernels cap the CTAs per SM: forward 2, dQ 4, dK/dV 2
   const int max_ctas = mode == 1 ? 4 : 2;
   static const double overlap[5] = {0.0, 1.0, 1.7, 2.3, 2.8};
@@ -200,11 +205,20 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
       const int acc_cols = mode == 1 ? g.D : 2 * g.D;
       const int s_regions = 2;
       if (cap * s_regions > tmem_cols - acc_cols || cap > kMaxCols) continue;
+      if (max_cols >= 32 && cap > max_cols) continue;
       FwdParams p = base;
       const long long cost = choose_tile(g, p, cap, mode);
       if (cost < 0) continue;
-      p.q_stages = 2; p.kv_stages = mode == 0 ? 3 : 2;
-      if (smem_needed(p) > smem_limit) p.kv_stages = 2;
+      p.q_stages = 2; p.kv_stages = 2; p.n_sbuf = 2;
+      if (mode == 0) {
+        // as many S/P buffers as tensor memory holds (a warp with little work in a chunk runs
+        // ahead of the others by up to n_sbuf - 1 chunks), one more K/V stage than that
+        p.n_sbuf = (tmem_cols - acc_cols) / p.n_pad;
+        if (p.n_sbuf > 6) p.n_sbuf = 6;
+        if (max_sbuf >= 2 && p.n_sbuf > max_sbuf) p.n_sbuf = max_sbuf;
+        p.kv_stages = p.n_sbuf + 1 > 6 ? 6 : p.n_sbuf + 1;
+        while (p.kv_stages > 2 && smem_needed(p) > smem_limit) --p.kv_stages;
+      }
       if (smem_needed(p) > smem_limit) p.q_stages = 1;
       if (smem_needed(p) > smem_limit) continue;           // a single K/V stage would lose the prefetch
       const double eff = (double)cost / overlap[ctas];
