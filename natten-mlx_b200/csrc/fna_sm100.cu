@@ -101,7 +101,7 @@ size_t smem_needed(const FwdParams& p) {
   const size_t q = (size_t)p.q_stages * row_tiles * p.ndblk * kTileM * p.row_bytes;
   const size_t kv = (size_t)p.kv_stages * 2 * p.ndblk * p.n_pad * p.row_bytes;
   const size_t stats = p.mode == 2 ? (size_t)p.kv_stages * 2 * p.n_pad * 4 : 0;   // per-column lse / delta
-  return 1024 /*alignment slack*/ + q + kv + stats + (size_t)kMaxWords * 128 * 4 + 512;
+  return 1024 /*alignment slack*/ + q + kv + stats + (size_t)kMaxWords * 128 * 4 + 2560 /*barriers, work items, window tables*/;
 }
 
 // Best query tile for a cap of `nmax` S columns per chunk; returns the cost
@@ -193,6 +193,8 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
   const int max_cols = env_cols != nullptr ? atoi(env_cols) : 0;
   const char* env_sbuf = getenv("NATTEN_B200_MAX_SBUF");
   const int max_sbuf = env_sbuf != nullptr ? atoi(env_sbuf) : 0;
+  const char* env_minsb = getenv("NATTEN_B200_MIN_SBUF");
+  const int min_sbuf = env_minsb != nullptr ? atoi(env_minsb) : 0;
   // registers per thread of the kernels cap the CTAs per SM: forward 2, dQ 4, dK/dV 2
   const int max_ctas = mode == 1 ? 4 : 2;
   static const double overlap[5] = {0.0, 1.0, 1.7, 2.3, 2.8};
@@ -201,32 +203,38 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
     const int tmem_cols = ctas >= 3 ? 128 : 512 / ctas;   // a power of two per CTA
     const size_t smem_limit = (size_t)(232448 / ctas) - 1024;
     for (int cap : caps) {
-      // forward: S/P and O double-buffered; backward: S and dP regions, single-buffered accumulators
+      if (cap > kMaxCols || (max_cols >= 32 && cap > max_cols)) continue;
+      // forward: S/P ring (>= 2 buffers) and two O buffers; backward: one or two S+dP buffers
+      // and single accumulators
       const int acc_cols = mode == 1 ? g.D : 2 * g.D;
-      const int s_regions = 2;
-      if (cap * s_regions > tmem_cols - acc_cols || cap > kMaxCols) continue;
-      if (max_cols >= 32 && cap > max_cols) continue;
-      FwdParams p = base;
-      const long long cost = choose_tile(g, p, cap, mode);
-      if (cost < 0) continue;
-      p.q_stages = 2; p.kv_stages = 2; p.n_sbuf = 2;
-      if (mode == 0) {
-        // as many S/P buffers as tensor memory holds (a warp with little work in a chunk runs
-        // ahead of the others by up to n_sbuf - 1 chunks), one more K/V stage than that
-        p.n_sbuf = (tmem_cols - acc_cols) / p.n_pad;
-        if (p.n_sbuf > 6) p.n_sbuf = 6;
-        if (max_sbuf >= 2 && p.n_sbuf > max_sbuf) p.n_sbuf = max_sbuf;
-        p.kv_stages = p.n_sbuf + 1 > 6 ? 6 : p.n_sbuf + 1;
+      for (int nb = 2; nb >= (mode == 0 ? 2 : 1); --nb) {
+        if (mode != 0 && max_sbuf >= 1 && nb > max_sbuf) continue;
+        if (mode != 0 && min_sbuf >= 1 && nb < min_sbuf) continue;
+        const int s_regions = mode == 0 ? nb : 2 * nb;
+        if (cap * s_regions > tmem_cols - acc_cols) continue;
+        FwdParams p = base;
+        const long long cost = choose_tile(g, p, cap, mode);
+        if (cost < 0) continue;
+        p.q_stages = 2; p.kv_stages = 4; p.n_sbuf = nb;   // backward: up to four chunk-operand stages
+        if (mode == 0) {
+          // as many S/P buffers as tensor memory holds (a warp with little work in a chunk runs
+          // ahead of the others by up to n_sbuf - 1 chunks), one more K/V stage than that
+          p.n_sbuf = (tmem_cols - acc_cols) / p.n_pad;
+          if (p.n_sbuf > 6) p.n_sbuf = 6;
+          if (max_sbuf >= 2 && p.n_sbuf > max_sbuf) p.n_sbuf = max_sbuf;
+          p.kv_stages = p.n_sbuf + 1 > 6 ? 6 : p.n_sbuf + 1;
+        }
         while (p.kv_stages > 2 && smem_needed(p) > smem_limit) --p.kv_stages;
-      }
-      if (smem_needed(p) > smem_limit) p.q_stages = 1;
-      if (smem_needed(p) > smem_limit) continue;           // a single K/V stage would lose the prefetch
-      const double eff = (double)cost / overlap[ctas];
-      if (best < 0 || eff < best) {
-        best = eff;
-        p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - 2 * g.D;
-        p.dp_col = p.n_pad; p.acc_col = tmem_cols - acc_cols; p.acc2_col = tmem_cols - g.D;
-        pl.p = p;
+        if (smem_needed(p) > smem_limit) p.q_stages = 1;
+        if (smem_needed(p) > smem_limit) continue;           // a single chunk stage would lose the prefetch
+        // a second S+dP buffer hides the tensor-core round trip of a chunk
+        const double eff = (double)cost / overlap[ctas] * (mode != 0 && nb == 1 ? 1.25 : 1.0);
+        if (best < 0 || eff < best) {
+          best = eff;
+          p.ctas_per_sm = ctas; p.tmem_cols = tmem_cols; p.ocol = tmem_cols - 2 * g.D;
+          p.dp_col = p.n_pad; p.acc_col = tmem_cols - acc_cols; p.acc2_col = tmem_cols - g.D;
+          pl.p = p;
+        }
       }
     }
   }

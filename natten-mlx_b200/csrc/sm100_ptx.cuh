@@ -56,6 +56,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 constexpr uint32_t kSpinLimit = 4000;  // try_wait calls (about 1 ms each at most) before a wait gives up
 
+// Non-blocking probe of a phase.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P1;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+constexpr uint32_t kPollLimit = 2048;  // probes before a wait on the critical path starts to sleep
+
 // Waits for the phase with the given parity.  Returns false when the CTA is
 // aborting (this wait ran out, or another one did before).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -65,6 +80,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+
+// The same for the waits between the MMA thread and the warps that feed it: a sleeping
+// thread takes a few hundred cycles to wake, so the phase is polled first (a bounded number
+// of probes) and the sleeping wait takes over only when the phase is far away.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < kPollLimit; ++it)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag);
 }
 
 // ---- TMA ----------------------------------------------------------------------
