@@ -106,7 +106,7 @@ def algorithmic_bytes(w):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of one forward+backward call of
 # the default workload; workloads without a capture report null.
-NCU_TRAFFIC = {"na2d_nat_stage": {"fna_fwd_sm100": 86.1e6, "fna_bwd_dq_sm100": 118.6e6, "fna_bwd_dkv_sm100": 129.4e6,
+NCU_TRAFFIC = {"na2d_nat_stage": {"fna_fwd_sm100": 84.3e6, "fna_bwd_dq_sm100": 117.2e6, "fna_bwd_dkv_sm100": 130.2e6,
                                   "fna_bwd_prep_sm100": 51.5e6}}
 
 
@@ -263,22 +263,17 @@ def run_ours(args, w, rank, world, local_rank):
     # end-to-end: pinned host buffers -> device -> public API forward + backward -> host
     host_in = [make_inputs(w, 1234 + vi, dev, pinned=True) for vi in range(nvar)]
     host_out = [[torch.empty_like(t).pin_memory() for t in (hi[0], hi[0], hi[1], hi[2])] for hi in host_in]
-    stage = [[torch.empty(t.shape, dtype=t.dtype, device=dev) for t in hi] for hi in host_in]
-    fused = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[rank_nd]
     h2d = sum(t.numel() * t.element_size() for hi in host_in for t in hi)
     d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
 
+    # one streaming plan per variant: batch slabs travel in, are computed and travel out concurrently
+    from natten_mlx_b200.host import HostPipeline
+    pipes = [HostPipeline(w["shape"], host_in[0][0].dtype, dev, w["kernel"], dilation=dil, is_causal=w["causal"],
+                          heads_kv=w["heads_kv"], slabs=8) for dil in w["dilations"]]
+
     def step_e2e():
-        for hi, ho, st, dil in zip(host_in, host_out, stage, w["dilations"]):
-            for s, h in zip(st, hi):
-                s.copy_(h, non_blocking=True)
-            q, k, v = (t.requires_grad_(True) for t in st[:3])
-            out = fused(q, k, v, kernel_size=w["kernel"], dilation=dil, is_causal=w["causal"])
-            dq, dk, dv = torch.autograd.grad(out, (q, k, v), st[3])
-            for h, d in zip(ho, (out.detach(), dq, dk, dv)):
-                h.copy_(d, non_blocking=True)
-            for t in st[:3]:
-                t.requires_grad_(False)
+        for hi, ho, pipe in zip(host_in, host_out, pipes):
+            pipe.run(hi[0], hi[1], hi[2], hi[3], ho[0], ho[1], ho[2], ho[3])
 
     def barrier():
         if world > 1:
