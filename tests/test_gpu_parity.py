@@ -332,7 +332,8 @@ def test_full_size_properties_na2d_bf16():
         # fused == split composition, and lse == logsumexp of the split logits
         logits = nb.na2d_qk(q, k, 7, dil).float()
         o_split = nb.na2d_av(torch.softmax(logits, -1).to(torch.bfloat16), v, 7, dil)
-        assert (o.float() - o_split.float()).abs().max() < 3e-2
+        # both sides round probabilities and outputs to bf16: 2e-2 of the largest magnitude, as everywhere
+        assert (o.float() - o_split.float()).abs().max() / o.float().abs().max() < 2e-2
         assert (lse - torch.logsumexp(logits, -1)).abs().max() < 3e-2
         # gradient identities: sum_keys dV = sum_queries dO ; sum q.dq = sum k.dk (rows of dS sum to zero)
         _, (dq, dk, dv) = grads_of(lambda a, b, c: nb.na2d(a, b, c, kernel_size=7, dilation=dil), [q, k, v], cot)
