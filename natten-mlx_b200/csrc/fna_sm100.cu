@@ -20,6 +20,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include <cstdio>
 #include <mutex>
 
 #include "fna_sm100.cuh"
@@ -110,11 +111,13 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
   int lgmax[3];
   for (int a = 0; a < 3; ++a) lgmax[a] = ceil_div(g.ge[a], g.dl[a]);
   long long best_cost = -1;
+  int want[3] = {0, 0, 0};                       // tuning aid: pin the tile shape ("t0,t1,t2")
+  if (const char* env_tile = getenv("NATTEN_B200_TILE")) sscanf(env_tile, "%d,%d,%d", &want[0], &want[1], &want[2]);
   for (int t2 = 1; t2 <= p.P; t2 *= 2)
     for (int t1 = 1; t1 * t2 <= p.P; t1 *= 2) {
       const int t0 = p.P / (t1 * t2);
       const int T[3] = {t0, t1, t2};
-      bool skip = false;
+      bool skip = want[2] > 0 && (t0 != want[0] || t1 != want[1] || t2 != want[2]);
       int box[3];
       for (int a = 0; a < 3; ++a) {
         if (g.ge[a] == 1 && T[a] != 1) skip = true;          // nothing to tile on a trivial axis

@@ -1,0 +1,64 @@
+"""Leading-axis sharding with the K/V halo exchange on real GPUs (NCCL point-to-point):
+every rank holds its planes of a 3-D volume, calls ``sharding.na_sharded`` forward and
+backward, and its planes of the output and of dq/dk/dv must equal the unsharded result of the
+same kernels on one GPU.  Needs two or more GPUs; on a single-GPU box the test is skipped (the
+same logic runs among CPU ranks in tests/test_sharding_gloo.py and as a one-GPU slab emulation
+in tests/test_gpu_parity.py)."""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, causal, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import natten_mlx_b200 as nb
+        from natten_mlx_b200 import sharding
+        T, ks, dl, ca = 12, (3, 3, 5), (2, 1, 1), (causal, False, False)
+        gen = torch.Generator().manual_seed(21)
+        full = [torch.randn((1, T, 6, 9, 2, 16), generator=gen) for _ in range(4)]      # q, k, v, cotangent
+        bounds = sharding.shard_bounds(T, world)
+        lo, hi = bounds[rank], bounds[rank + 1]
+        dev = torch.device("cuda", rank)
+        q, k, v = (t[:, lo:hi].to(dev).requires_grad_(True) for t in full[:3])
+        out = sharding.na_sharded(q, k, v, T, ks, dl, ca)
+        out.backward(full[3][:, lo:hi].to(dev))
+        # the unsharded result on this rank's GPU
+        qf, kf, vf = (t.to(dev).requires_grad_(True) for t in full[:3])
+        ref = nb.na3d(qf, kf, vf, kernel_size=ks, dilation=dl, is_causal=ca)
+        ref.backward(full[3].to(dev))
+        ok = [torch.allclose(out, ref[:, lo:hi], atol=1e-5, rtol=1e-5)]
+        for a, b in ((q, qf), (k, kf), (v, vf)):
+            ok.append(torch.allclose(a.grad, b.grad[:, lo:hi], atol=1e-4, rtol=1e-4))
+        results[rank] = tuple(bool(x) for x in ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("causal", [True, False])
+def test_na_sharded_matches_unsharded_over_nccl(causal):
+    world = min(torch.cuda.device_count(), 4)
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), causal, results), nprocs=world, join=True)
+    assert len(results) == world
+    for r in range(world):
+        assert results[r] == (True, True, True, True), (r, results[r])
