@@ -371,14 +371,130 @@ def run_ours(args, w, rank, world, local_rank):
     print(json.dumps(line))
 
 
+# ---------------------------------------------------------------------------
+# table workloads (BASELINE configs 3 and 5): device-resident, single GPU, no CPU or end-to-end leg
+# ---------------------------------------------------------------------------
+TABLE_WORKLOADS = ("allin1_1d", "na2d_varlen_gqa")
+
+
+def run_table_workload(args):
+    import natten_mlx_b200 as nb
+    from natten_mlx_b200 import _lib
+    from natten_mlx_b200.extras.allin1 import na1d_av_fused, na1d_qk_rpb
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(1236)
+    rnd = lambda shape, dt: torch.randn(shape, generator=gen, dtype=torch.float32).to(dt).to(dev)
+    if args.workload == "allin1_1d":
+        # q, k, v [8,4096,4,12] fp32, rpb [4,9] ~ N(0,0.02), K=5, dilation 2, scale 0.288: QK+RPB -> softmax -> AV
+        q, k, v = (rnd((8, 4096, 4, 12), torch.float32) for _ in range(3))
+        rpb = rnd((4, 9), torch.float32) * 0.02
+        label = "allin1 fp32 na1d_qk_rpb -> softmax -> na1d_av_fused, B=8 L=4096 H=4 D=12 K=5 dilation 2"
+        tens = 8 * 4096 * 4 * 12 * 4
+        logit = 8 * 4096 * 4 * 5 * 4
+        byts = (2 * tens + logit) + 2 * logit + (logit + 2 * tens)       # QK ; softmax ; AV
+        flops = 2 * 4.0 * 8 * 4 * 4096 * 5 * 12 / 2                      # 2*N*K*D for QK and again for AV
+
+        def eager():
+            with torch.no_grad():
+                a = torch.softmax(na1d_qk_rpb(q, k, rpb, 5, 2, scale=0.288), dim=-1)
+                return na1d_av_fused(a, v, 5, 2)
+        # three launches of a few microseconds each: replayed from a CUDA graph (the eager time is reported too)
+        for _ in range(3):
+            eager()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = eager()
+        step = graph.replay
+        extra_cfg = {"launch": "CUDA graph replay of the three launches"}
+        dtype = "f32"
+    else:
+        # B=16 padded to 128x128, per-sample H,W from {64,...,128}, 16 query / 4 KV heads, D=128, K=13, dilation 2,
+        # 64 extra tokens, LSE returned and merged; forward + backward
+        B, M, Hq, Hkv, D, NX = 16, 128, 16, 4, 128, 64
+        sizes = (torch.randint(0, 9, (B, 2), generator=gen) * 8 + 64).to(torch.int32)
+        bf = torch.bfloat16
+        q = rnd((B, M, M, Hq, D), bf).requires_grad_(True)
+        k, v = (rnd((B, M, M, Hkv, D), bf).requires_grad_(True) for _ in range(2))
+        ak, av = (rnd((B, NX, Hkv, D), bf).requires_grad_(True) for _ in range(2))
+        cot = rnd((B, M, M, Hq, D), bf)
+        host_sizes = [tuple(int(x) for x in r) for r in sizes.tolist()]
+        st = sizes.to(dev)
+        tokens = sum(h * w_ for h, w_ in host_sizes)
+        label = (f"na2d bf16 varlen B=16 max 128x128 ({tokens} tokens) 16q/4kv heads D=128 K=13x13 dilation 2, "
+                 "64 extra tokens, lse+merge, fwd+bwd")
+        flops = 3.5 * 4.0 * Hq * tokens * (169 + NX) * D
+        byts = None
+
+        def step():
+            out = nb.na2d_varlen(q, k, v, st, 13, 2, additional_keys=ak, additional_values=av, host_sizes=host_sizes)
+            return torch.autograd.grad(out, (q, k, v, ak, av), cot)
+        eager, extra_cfg = None, {}
+        dtype = "bf16"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = _lib.launch_count()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    for a, b in evs:
+        flush.zero_()
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    launches = _lib.launch_count() - launches0
+    if eager is not None:                    # the same step launched eagerly, for the record
+        launches = 2 * args.steps            # graph replays bypass the library's launch counter
+        for a, b in evs:
+            flush.zero_()
+            a.record()
+            eager()
+            b.record()
+        torch.cuda.synchronize()
+        extra_cfg["ms_per_step_eager"] = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    clocks = sampler.stop()
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peaks = json.load(fh)
+    except OSError:
+        pass
+    roofline = None
+    if byts is not None:
+        hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+        ach = byts / (ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "whole step (3 launches)", "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": ach / hbm_peak, "traffic": None, "peak_kind": "measured" if "hbm_gbs" in peaks else "fallback",
+                    "algorithmic_bytes_per_step": byts}
+    print(json.dumps({
+        "metric": "na_fwd_bwd_effective_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": dict({"workload": label, "l2": "256 MiB buffer written between timed iterations",
+                        "kernel_family": _lib.last_path()}, **extra_cfg),
+        "roofline": roofline, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="na2d_nat_stage", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="na2d_nat_stage", choices=sorted(WORKLOADS) + list(TABLE_WORKLOADS))
     args = ap.parse_args()
+    if args.workload in TABLE_WORKLOADS:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "table workloads have no reference arm"}))
+        elif int(os.environ.get("RANK", "0")) == 0:
+            run_table_workload(args)
+        return
     w = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
