@@ -65,6 +65,18 @@ enum {
  * valid extent of each sample inside the padded tensors (variable-size
  * batches); it replaces global_extent per sample, and queries outside it
  * produce zeros.
+ *
+ * mem_extent, when not all zero, says that every tensor of the call (q, k, v,
+ * out, lse and the gradients) is the leading corner of a larger dense array
+ * with spatial extents mem_extent >= global_extent: positions are as far
+ * apart in memory as in that larger array, the window arithmetic and the
+ * bounds use global_extent, and nothing outside the corner is read or
+ * written.  This is how one sample of a padded variable-size batch is handed
+ * to the tensor-core kernels (one call per sample, pointers at the sample, so
+ * that padding of any content, NaN included, stays out of the arithmetic;
+ * the reference slices the sample out, src/natten_mlx/_core/pure.py:559-577).
+ * Only the fused entry points take it, only on the tensor-core kernels, and
+ * not together with slabs, extents or extra tokens (NATTEN_B200_EINVAL).
  */
 typedef struct natten_b200_geom {
   int32_t rank;             /* 1, 2 or 3                                          */
@@ -86,6 +98,8 @@ typedef struct natten_b200_geom {
   int32_t n_extra;          /* tokens in k_extra / v_extra, 0 if none            */
   int32_t path;             /* NATTEN_B200_PATH_*                                */
   const int32_t* extents;   /* device, [batch, rank], or NULL                     */
+  int32_t mem_extent[3];    /* all zero: dense tensors; see above                 */
+  int32_t reserved;         /* must be zero                                       */
 } natten_b200_geom;
 
 int natten_b200_abi_version(void);

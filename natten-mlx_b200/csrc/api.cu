@@ -17,7 +17,8 @@
 #include <stddef.h>
 
 // The ctypes mirror of the geometry struct relies on this layout.
-static_assert(sizeof(natten_b200_geom) == 152, "natten_b200_geom layout changed");
+static_assert(sizeof(natten_b200_geom) == 168, "natten_b200_geom layout changed");
+static_assert(offsetof(natten_b200_geom, mem_extent) == 152, "natten_b200_geom layout changed");
 static_assert(offsetof(natten_b200_geom, scale) == 132, "natten_b200_geom layout changed");
 static_assert(offsetof(natten_b200_geom, extents) == 144, "natten_b200_geom layout changed");
 
@@ -100,6 +101,8 @@ int make_geo(const natten_b200_geom* in, Geo* g) {
     g->ca[a] = 0;
   }
   bool sharded = false;
+  g->pitched = false;
+  for (int i = 0; i < in->rank; ++i) g->pitched = g->pitched || in->mem_extent[i] != 0;
   for (int i = 0; i < in->rank; ++i) {
     const int a = lead + i;
     g->qe[a] = in->q_extent[i]; g->ke[a] = in->kv_extent[i]; g->ge[a] = in->global_extent[i];
@@ -143,6 +146,18 @@ int make_geo(const natten_b200_geom* in, Geo* g) {
   }
   if (sharded && in->extents != nullptr)
     return set_error(NATTEN_B200_EINVAL, "per-sample extents cannot be combined with a sharded slab");
+  for (int a = 0; a < 3; ++a) g->me[a] = g->ge[a];
+  if (g->pitched) {
+    if (sharded || in->extents != nullptr || in->n_extra != 0)
+      return set_error(NATTEN_B200_EINVAL, "mem_extent cannot be combined with slabs, per-sample extents or extra tokens");
+    for (int i = 0; i < in->rank; ++i) {
+      if (in->mem_extent[i] < in->global_extent[i])
+        return set_error(NATTEN_B200_EINVAL, "mem_extent[%d]=%d is smaller than the extent %d", i, in->mem_extent[i],
+                         in->global_extent[i]);
+      if (in->stride[i] != 1) return set_error(NATTEN_B200_EINVAL, "mem_extent needs stride 1");
+      g->me[lead + i] = in->mem_extent[i];
+    }
+  }
   long long n_out = 1, n_q = 1, n_kv = 1, kvol = 1;
   for (int a = 0; a < 3; ++a) {
     g->out[a] = (g->qe[a] + g->st[a] - 1) / g->st[a];
@@ -152,7 +167,8 @@ int make_geo(const natten_b200_geom* in, Geo* g) {
   if (kvol > (1 << 20)) return set_error(NATTEN_B200_EINVAL, "kernel volume %lld is too large", kvol);
   g->kvol = (int)kvol;
   const long long lim = 0x7fffffffLL;
-  if (g->B * n_q * g->Hq > lim || g->B * n_kv * g->Hkv > lim || g->B * n_out * g->Hq > lim)
+  if (g->B * n_q * g->Hq > lim || g->B * n_kv * g->Hkv > lim || g->B * n_out * g->Hq > lim ||
+      (long long)g->B * g->me[0] * g->me[1] * g->me[2] * g->Hq > lim)
     return set_error(NATTEN_B200_EINVAL, "problem has more than 2^31 rows");
   return NATTEN_B200_OK;
 }
@@ -226,10 +242,16 @@ int natten_b200_axis_table(int32_t length, int32_t kernel, int32_t dilation, int
   return NATTEN_B200_OK;
 }
 
+static int reject_pitched(const Geo& g, const char* what) {
+  return g.pitched ? set_error(NATTEN_B200_EINVAL, "%s: mem_extent is only taken by the fused entry points", what)
+                   : NATTEN_B200_OK;
+}
+
 int natten_b200_qk_forward(const natten_b200_geom* gi, const void* q, const void* k,
                            const float* bias, void* logits, void* stream) {
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;
+  if (int rc = reject_pitched(g, "qk_forward")) return rc;
   if (any_null({q, k, logits})) return set_error(NATTEN_B200_EINVAL, "qk_forward: null tensor");
   if (bias != nullptr) {
     for (int a = 0; a < 3; ++a)
@@ -242,6 +264,7 @@ int natten_b200_qk_backward(const natten_b200_geom* gi, const void* q, const voi
                             const void* dlogits, void* dq, void* dk, float* dbias, void* stream) {
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;
+  if (int rc = reject_pitched(g, "qk_backward")) return rc;
   if (any_null({q, k, dlogits, dq, dk})) return set_error(NATTEN_B200_EINVAL, "qk_backward: null tensor");
   return run_split(SplitOp::QkBackward, g, gi->dtype, q, k, dlogits, nullptr, dq, dk, dbias, (cudaStream_t)stream);
 }
@@ -250,6 +273,7 @@ int natten_b200_av_forward(const natten_b200_geom* gi, const void* attn, const v
                            void* stream) {
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;
+  if (int rc = reject_pitched(g, "av_forward")) return rc;
   if (any_null({attn, v, out})) return set_error(NATTEN_B200_EINVAL, "av_forward: null tensor");
   return run_split(SplitOp::AvForward, g, gi->dtype, attn, v, nullptr, nullptr, out, nullptr, nullptr, (cudaStream_t)stream);
 }
@@ -258,6 +282,7 @@ int natten_b200_av_backward(const natten_b200_geom* gi, const void* attn, const 
                             const void* dout, void* dattn, void* dv, void* stream) {
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;
+  if (int rc = reject_pitched(g, "av_backward")) return rc;
   if (any_null({attn, v, dout, dattn, dv})) return set_error(NATTEN_B200_EINVAL, "av_backward: null tensor");
   return run_split(SplitOp::AvBackward, g, gi->dtype, attn, v, dout, nullptr, dattn, dv, nullptr, (cudaStream_t)stream);
 }
@@ -280,6 +305,9 @@ int natten_b200_fused_forward(const natten_b200_geom* gi, const void* q, const v
     set_last_path("tcgen05");
     return run_fused_forward_sm100(g, gi->dtype, a, (cudaStream_t)stream);
   }
+  if (g.pitched)
+    return set_error(NATTEN_B200_EINVAL, "fused_forward: mem_extent needs the tensor-core kernels, which do not take this shape: %s",
+                     sm100_unsupported_reason(g, gi->dtype));
   set_last_path("simt");
   return run_fused_forward_simt(g, gi->dtype, a, (cudaStream_t)stream);
 }
@@ -319,6 +347,9 @@ int natten_b200_fused_backward(const natten_b200_geom* gi, const void* q, const 
     set_last_path("tcgen05");
     return run_fused_backward_sm100(g, gi->dtype, a, (cudaStream_t)stream);
   }
+  if (g.pitched)
+    return set_error(NATTEN_B200_EINVAL, "fused_backward: mem_extent needs the tensor-core kernels, which do not take this shape: %s",
+                     sm100_unsupported_reason(g, gi->dtype));
   set_last_path("simt");
   return run_fused_backward_simt(g, gi->dtype, a, (cudaStream_t)stream);
 }

@@ -22,6 +22,7 @@
 
 #include <cstdio>
 #include <mutex>
+#include <vector>
 
 #include "fna_sm100.cuh"
 #include "sm100_ptx.cuh"
@@ -57,6 +58,7 @@ struct FwdParams {
   int B, Hq, Hkv, rep, D;
   int rank;              // spatial rank of the tensors (tensor-map rank = rank + 2)
   int L[3], K[3], dl[3], ca[3];
+  int M[3];                           // extents behind the memory strides (== L for dense tensors)
   int T[3];              // query tile extents in class coordinates
   int hpt, P;            // heads per tile, positions per tile (hpt * P == 128)
   int box[3];            // key box extents
@@ -105,6 +107,49 @@ size_t smem_needed(const FwdParams& p) {
   return 1024 /*alignment slack*/ + q + kv + stats + (size_t)kMaxWords * 128 * 4 + 2560 /*barriers, work items, window tables*/;
 }
 
+// Window of query i of a dilation class in class coordinates (the host twin of class_window()
+// in the kernels): valid keys are [max(s, 0), e).
+void host_class_window(int i, int g, int lg, int L, int K, int d, int& s, int& e) {
+  if (d == 1) {
+    s = window_start(i, L, K, 1);
+  } else {
+    const int start = window_start(i * d + g, L, K, d);
+    s = (start - g) / d;
+  }
+  e = s + K < lg ? s + K : lg;
+}
+
+// Largest number of consecutive queries whose windows hold some key of a tile of T keys on one
+// axis with a centred window: windows pulled inward at the two ends of the axis are also held
+// by queries further in, so near the ends a key tile is addressed from more than T + K - 1
+// queries (by up to K / 2 more when the tile starts within the first K keys).  Exact, by
+// walking every tile of every dilation class.
+int max_query_span(int L, int K, int d, int T) {
+  int best = 0;
+  for (int g = 0; g < d && g < L; ++g) {
+    const int lg = (L - g + d - 1) / d;
+    std::vector<int> lo(lg), hi(lg);           // per key: first query and one past the last query
+    for (int x = 0; x < lg; ++x) { lo[x] = lg; hi[x] = 0; }
+    for (int q = 0; q < lg; ++q) {
+      int s, e;
+      host_class_window(q, g, lg, L, K, d, s, e);
+      for (int x = s < 0 ? 0 : s; x < e; ++x) {
+        if (q < lo[x]) lo[x] = q;
+        if (q + 1 > hi[x]) hi[x] = q + 1;
+      }
+    }
+    for (int t = 0; t < lg; t += T) {
+      int a = lg, b = 0;
+      for (int x = t; x < t + T && x < lg; ++x) {
+        if (lo[x] < a) a = lo[x];
+        if (hi[x] > b) b = hi[x];
+      }
+      if (b - a > best) best = b - a;
+    }
+  }
+  return best;
+}
+
 // Best query tile for a cap of `nmax` S columns per chunk; returns the cost
 // (tiles x chunks x padded columns) or -1 when nothing fits.
 long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
@@ -121,9 +166,10 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
       int box[3];
       for (int a = 0; a < 3; ++a) {
         if (g.ge[a] == 1 && T[a] != 1) skip = true;          // nothing to tile on a trivial axis
-        // keys a query tile addresses: T + K - 1; queries that address a key tile: one more at
-        // most, because windows pulled inward at an edge also cover keys further in
-        const int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1 + ((mode == 2 && g.ca[a] == 0) ? 1 : 0);
+        // keys a query tile addresses: T + K - 1; queries that address a key tile: more near the
+        // ends of the axis (see max_query_span)
+        int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1;
+        if (mode == 2 && g.ca[a] == 0) need = max_query_span(g.ge[a], g.K[a], g.dl[a], T[a]);
         box[a] = need < lgmax[a] ? need : lgmax[a];
         if (box[a] > 256) skip = true;                        // TMA box limit
       }
@@ -175,7 +221,7 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
   }
   if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
   base.B = g.B; base.Hq = g.Hq; base.Hkv = g.Hkv; base.rep = g.rep; base.D = g.D; base.rank = g.rank;
-  for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
+  for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.M[a] = g.me[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
   base.mode = mode;
   base.hpt = mode == 2 ? 1 : ((g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1));
   base.head_groups = mode == 2 ? 1 : g.rep / base.hpt;
@@ -291,7 +337,7 @@ int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, i
   const cuuint32_t trank = (cuuint32_t)(p.rank + 2);
   long long stride_el[3];  // elements between consecutive coordinates on each axis
   long long s = (long long)heads * p.D;
-  for (int a = 2; a >= 0; --a) { stride_el[a] = s; s *= p.L[a]; }
+  for (int a = 2; a >= 0; --a) { stride_el[a] = s; s *= p.M[a]; }
   const long long batch_el = s;
   int ci = 0;
   for (int g0 = 0; g0 < p.dl[0]; ++g0)

@@ -76,6 +76,8 @@ struct Geo {
   int B, Hq, Hkv, rep, D;
   int rank;            // original rank, used to index `extents`
   int qe[3], ke[3], ge[3], qo[3], ko[3];
+  int me[3];           // extents that give the memory strides (== ge unless the tensors are corners of larger arrays)
+  bool pitched;
   int K[3], st[3], dl[3], ca[3], out[3];
   int kvol, n_extra;
   float scale;

@@ -228,6 +228,74 @@ def fused_backward(q, k, v, out, lse, grad_out, grad_lse, ks, st, dl, ca, scale,
 
 
 # ---------------------------------------------------------------------------
+# variable-size batches on the tensor-core kernels: one call per sample
+# ---------------------------------------------------------------------------
+# The kernels take a sample as the leading corner of its padded block
+# (``mem_extent`` of the C geometry): strides come from the padded extents,
+# bounds and windows from the sample's own, so padding of any content stays
+# out of the arithmetic and is never written.  The reference slices each
+# sample out and pads the result (src/natten_mlx/_core/pure.py:559-577).
+
+def _sample_geom(q, k, rank, size, ks, dl, scale):
+    one, no = (1,) * rank, (False,) * rank
+    return _lib.make_geom(rank, 1, q.shape[-2], k.shape[-2], q.shape[-1], _DTYPES[q.dtype], size, ks, one, dl, no,
+                          scale, path=_lib.PATH_TCGEN05, mem_extent=tuple(q.shape[1:1 + rank]))
+
+
+def per_sample_tensor_core_ok(q, k, host_sizes, ks, dl, scale) -> bool:
+    """True when every sample size has tensor-core plans for the forward and both backward kernels."""
+    if _fused_path == "simt" or not q.is_cuda or q.dtype not in (torch.float16, torch.bfloat16):
+        return False
+    rank = q.dim() - 3
+    for size in sorted(set(tuple(int(x) for x in s) for s in host_sizes)):
+        try:
+            plan = _lib.describe_plan(_sample_geom(q, k, rank, size, ks, dl, _scale(scale, q.shape[-1])))
+        except ValueError:
+            return False
+        if "unsupported" in plan:
+            return False
+    return True
+
+
+def fused_forward_per_sample(q, k, v, host_sizes, ks, dl, scale):
+    """(out, lse) with zeros in the padding; q/k/v ``[B, padded spatial..., heads, D]``."""
+    rank = q.dim() - 3
+    q, k, v = _prep(q, k, v)
+    out = torch.zeros_like(q)
+    lse = torch.zeros(q.shape[:-1], dtype=torch.float32, device=q.device)
+    lib, sc = _lib.load(), _scale(scale, q.shape[-1])
+    with torch.cuda.device(q.device):
+        stream = _stream(q)
+        for b, size in enumerate(host_sizes):
+            g = _sample_geom(q, k, rank, tuple(int(x) for x in size), ks, dl, sc)
+            _lib.check(lib.natten_b200_fused_forward(g, _ptr(q[b]), _ptr(k[b]), _ptr(v[b]), None, None, _ptr(out[b]),
+                                                     _ptr(lse[b]), stream))
+    return out, lse
+
+
+def fused_backward_per_sample(q, k, v, out, lse, grad_out, grad_lse, host_sizes, ks, dl, scale):
+    """(dq, dk, dv) with zeros in the padding."""
+    rank = q.dim() - 3
+    q, k, v, out, grad_out = _prep(q, k, v, out, grad_out)
+    lse = lse.contiguous()
+    if grad_lse is not None:
+        grad_lse = grad_lse.to(torch.float32).contiguous()
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    lib, sc = _lib.load(), _scale(scale, q.shape[-1])
+    geoms = [_sample_geom(q, k, rank, tuple(int(x) for x in size), ks, dl, sc) for size in host_sizes]
+    nbytes = max(int(lib.natten_b200_fused_backward_scratch_bytes(g)) for g in geoms)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)   # the calls run in stream order
+    with torch.cuda.device(q.device):
+        stream = _stream(q)
+        for b, g in enumerate(geoms):
+            _lib.check(lib.natten_b200_fused_backward(
+                g, _ptr(q[b]), _ptr(k[b]), _ptr(v[b]), None, None, _ptr(out[b]), _ptr(lse[b]), _ptr(grad_out[b]),
+                None if grad_lse is None else _ptr(grad_lse[b]), _ptr(dq[b]), _ptr(dk[b]), _ptr(dv[b]), None, None,
+                _ptr(scratch), nbytes, stream))
+    return dq, dk, dv
+
+
+# ---------------------------------------------------------------------------
 # merge
 # ---------------------------------------------------------------------------
 

@@ -45,6 +45,8 @@ class Geom(ctypes.Structure):
         ("n_extra", ctypes.c_int32),
         ("path", ctypes.c_int32),
         ("extents", ctypes.c_void_p),
+        ("mem_extent", _I3),
+        ("reserved", ctypes.c_int32),
     ]
 
 
@@ -157,7 +159,8 @@ def make_geom(rank: int, batch: int, heads_q: int, heads_kv: int, head_dim: int,
               dilation: Sequence[int], causal: Sequence[bool], scale: float, *,
               n_extra: int = 0, path: int = PATH_AUTO, extents_ptr: int = 0,
               q_extent: Optional[Sequence[int]] = None, kv_extent: Optional[Sequence[int]] = None,
-              q_offset: Optional[Sequence[int]] = None, kv_offset: Optional[Sequence[int]] = None) -> Geom:
+              q_offset: Optional[Sequence[int]] = None, kv_offset: Optional[Sequence[int]] = None,
+              mem_extent: Optional[Sequence[int]] = None) -> Geom:
     def arr(v, fill=0):
         v = list(v) + [fill] * (3 - len(v))
         return _I3(*[int(x) for x in v])
@@ -175,4 +178,6 @@ def make_geom(rank: int, batch: int, heads_q: int, heads_kv: int, head_dim: int,
     g.n_extra = int(n_extra)
     g.path = int(path)
     g.extents = extents_ptr or None
+    g.mem_extent = arr(mem_extent if mem_extent is not None else [0] * rank)
+    g.reserved = 0
     return g

@@ -42,6 +42,33 @@ class _FusedNA(torch.autograd.Function):
         return dq, dk, dv, dke, dve, None, None, None, None, None, None
 
 
+class _PerSampleNA(torch.autograd.Function):
+    """(out, lse) of a variable-size batch, one tensor-core call per sample; zeros in the padding."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, host_sizes, ks, dl, scale):
+        backend = ops._backend_module()
+        out, lse = backend.fused_forward_per_sample(q, k, v, host_sizes, ks, dl, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.params = (host_sizes, ks, dl, scale)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, grad_out, grad_lse):
+        q, k, v, out, lse = ctx.saved_tensors
+        host_sizes, ks, dl, scale = ctx.params
+        backend = ops._backend_module()
+        if grad_out is None:
+            grad_out = torch.zeros_like(out)
+        dq, dk, dv = backend.fused_backward_per_sample(q, k, v, out, lse, grad_out, grad_lse, host_sizes, ks, dl,
+                                                       scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def per_sample_with_grad(q, k, v, host_sizes, ks, dl, scale):
+    return _PerSampleNA.apply(q, k, v, host_sizes, ks, dl, scale)
+
+
 class _QK(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, rank, ks, st, dl, ca, scale):

@@ -34,7 +34,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_geom_struct_layout_matches_header():
     # the C side pins the same numbers with static_assert (csrc/api.cu)
-    assert ctypes.sizeof(_lib.Geom) == 152
+    assert ctypes.sizeof(_lib.Geom) == 168
     assert _lib.Geom.extents.offset == 144 and _lib.Geom.scale.offset == 132
 
 

@@ -42,6 +42,8 @@ CASES = [
     ((1, 5, 9, 12, 2, 32), 2, (3, 3, 5), (1, 1, 1), (False, False, False)),
     ((1, 20, 22, 8, 128), 2, (13, 13), (1, 1), (False, False)),      # GQA: 4 query heads packed per tile
     ((1, 12, 14, 4, 32), 2, (4, 6), (1, 1), (False, False)),         # even kernels
+    ((1, 24, 20, 4, 32), 4, (5, 7), (1, 1), (False, False)),         # key tiles narrower than the kernel (4 < 5)
+    ((1, 30, 23, 2, 32), 2, (7, 5), (1, 2), (False, False)),
     ((8, 64, 64, 8, 32), 8, (3, 3), (1, 1), (False, False)),         # 2048 tiles: every CTA walks several tiles
     ((6, 48, 40, 8, 64), 2, (5, 3), (2, 1), (False, True)),          # several tiles per CTA with packed heads
 ]
