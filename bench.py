@@ -272,8 +272,9 @@ def run_ours(args, w, rank, world, local_rank):
                           heads_kv=w["heads_kv"], slabs=8) for dil in w["dilations"]]
 
     def step_e2e():
-        for hi, ho, pipe in zip(host_in, host_out, pipes):
-            pipe.run(hi[0], hi[1], hi[2], hi[3], ho[0], ho[1], ho[2], ho[3])
+        for hi, ho, pipe in zip(host_in, host_out, pipes):      # the variants share the streams and keep streaming
+            pipe.run(hi[0], hi[1], hi[2], hi[3], ho[0], ho[1], ho[2], ho[3], wait=False)
+        pipes[-1].join()
 
     def barrier():
         if world > 1:

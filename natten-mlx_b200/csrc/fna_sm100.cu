@@ -19,8 +19,10 @@
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <cstdio>
+#include <map>
 #include <mutex>
 #include <vector>
 
@@ -204,7 +206,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
   return best_cost;
 }
 
-Plan make_plan(const Geo& g, int dtype, int mode = 0) {
+Plan make_plan_uncached(const Geo& g, int dtype, int mode) {
   Plan pl{};
   pl.ok = false;
   FwdParams base{};
@@ -302,6 +304,29 @@ Plan make_plan(const Geo& g, int dtype, int mode = 0) {
   p.idesc_pv = instr_desc(kTileM, g.D, fmt, 0, 1);
   pl.ok = true;
   pl.why = "";
+  return pl;
+}
+
+// Plans depend on the geometry only; building one walks tile shapes, chunk widths and (for the
+// dK/dV kernel) every key tile of every axis, which costs the host far more than a launch.
+Plan make_plan(const Geo& g, int dtype, int mode = 0) {
+  static const bool tuning = getenv("NATTEN_B200_CTAS_PER_SM") || getenv("NATTEN_B200_MAX_COLS") ||
+                             getenv("NATTEN_B200_MAX_SBUF") || getenv("NATTEN_B200_MIN_SBUF") || getenv("NATTEN_B200_TILE");
+  if (tuning) return make_plan_uncached(g, dtype, mode);
+  std::vector<int> key = {dtype, mode, g.B, g.Hq, g.Hkv, g.D, g.rank, g.n_extra, g.extents != nullptr ? 1 : 0};
+  int scale_bits;
+  memcpy(&scale_bits, &g.scale, sizeof(int));
+  key.push_back(scale_bits);
+  for (int a = 0; a < 3; ++a)
+    for (int v : {g.qe[a], g.ke[a], g.ge[a], g.me[a], g.qo[a], g.ko[a], g.K[a], g.st[a], g.dl[a], g.ca[a]}) key.push_back(v);
+  static std::mutex mu;
+  static std::map<std::vector<int>, Plan> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 4096) cache.clear();          // many distinct per-sample sizes: start over rather than grow
+  const Plan pl = make_plan_uncached(g, dtype, mode);
+  cache.emplace(std::move(key), pl);
   return pl;
 }
 

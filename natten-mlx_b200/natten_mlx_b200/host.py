@@ -26,6 +26,9 @@ from ._core import cuda as backend
 from .utils.params import normalize_kernel_size, normalize_tuple_param
 
 
+_STREAMS = {}
+
+
 class HostPipeline:
     """Reusable plan for ``fused forward + backward`` on host tensors of one geometry.
 
@@ -57,16 +60,25 @@ class HostPipeline:
         mk = lambda s: torch.empty((per,) + tuple(s[1:]), dtype=dtype, device=self.device)
         # two sets of device staging buffers: q, k, v, cotangent
         self.stage = [[mk(shape), mk(self.kv_shape), mk(self.kv_shape), mk(shape)] for _ in range(2)]
-        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(device=self.device) for _ in range(3))
+        # the three streams are shared by every plan of a device, so that consecutive runs of different
+        # plans keep streaming (the copy-in of the next run starts under the tail of the previous one)
+        key = (self.device.type, self.device.index if self.device.index is not None else torch.cuda.current_device())
+        if key not in _STREAMS:
+            _STREAMS[key] = tuple(torch.cuda.Stream(device=self.device) for _ in range(3))
+        self.s_in, self.s_cmp, self.s_out = _STREAMS[key]
+        self._free = [None, None]    # event: the compute stream has finished with staging set b
 
-    def run(self, q, k, v, dout, out, dq, dk, dv):
-        """All arguments are host tensors (pinned for overlap); the last four are written."""
+    def run(self, q, k, v, dout, out, dq, dk, dv, wait: bool = True):
+        """All arguments are host tensors (pinned for overlap); the last four are written.
+
+        With ``wait=False`` the current stream is not made to wait for the results: call
+        :meth:`join` (of the last plan run) before reading them.  Several runs may be queued."""
         if tuple(q.shape) != self.shape or tuple(k.shape) != self.kv_shape or tuple(v.shape) != self.kv_shape:
             raise ValueError("HostPipeline.run: tensor shapes do not match the plan")
         cur = torch.cuda.current_stream(self.device)
-        for s in (self.s_in, self.s_cmp, self.s_out):
+        for s in (self.s_in, self.s_cmp, self.s_out):      # work already queued on the current stream comes first
             s.wait_stream(cur)
-        free = [None, None]          # event: the compute stream has finished with staging set b
+        free = self._free
         for i, (b0, b1) in enumerate(self.ranges):
             n = b1 - b0
             st = self.stage[i % 2]
@@ -92,5 +104,11 @@ class HostPipeline:
                 for h, d in zip((out, dq, dk, dv), (o, gq, gk, gv)):
                     d.record_stream(self.s_out)
                     h[b0:b1].copy_(d, non_blocking=True)
+        if wait:
+            self.join()
+
+    def join(self):
+        """Make the current stream wait for everything queued on the pipeline's streams."""
+        cur = torch.cuda.current_stream(self.device)
         cur.wait_stream(self.s_cmp)
         cur.wait_stream(self.s_out)
