@@ -255,12 +255,13 @@ def _varlen(rank, query, key, value, sizes, kernel_size, dilation, scale, return
 def _varlen_tensor_core(rank, query, key, value, host, ks, dl, scale_value, add_k, add_v):
     """Variable-size batch on the tensor-core kernels: one call per sample for the neighbourhood
     branch; extra tokens as the reference composes them (functional.py:340-381): dense attention
-    over the extra tokens (a plain batched matrix product, float32 softmax) merged with the
-    neighbourhood branch through the log-sum-exps by the merge kernel."""
+    over the extra tokens (the library's scaled-dot-product kernel, as the reference's
+    ``mx.fast.scaled_dot_product_attention``) merged with the neighbourhood branch through the
+    log-sum-exps by the merge kernel."""
     out, lse = _ag.per_sample_with_grad(query, key, value, host, ks, dl, scale_value)
     if add_k is None:
         return out, lse
-    batch, heads_q, heads_kv, dim = query.shape[0], query.shape[-2], key.shape[-2], query.shape[-1]
+    batch, heads_q, dim = query.shape[0], query.shape[-2], query.shape[-1]
     spatial = tuple(query.shape[1:1 + rank])
     # rows inside each sample's extents (padding may hold anything: it is replaced by zeros before the product)
     mask = torch.ones((batch,) + spatial, dtype=torch.bool, device=query.device)
@@ -268,17 +269,12 @@ def _varlen_tensor_core(rank, query, key, value, host, ks, dl, scale_value, add_
         idx = torch.arange(spatial[a], device=query.device).view((1,) + (1,) * a + (-1,) + (1,) * (rank - 1 - a))
         lim = torch.tensor([s[a] for s in host], device=query.device).view((batch,) + (1,) * rank)
         mask = mask & (idx < lim)
-    rep = heads_q // heads_kv
-    outs, lses = [], []
-    for b in range(batch):            # sample by sample: the float32 logits of the whole batch can be large
-        q_b = torch.where(mask[b][..., None, None], query[b], torch.zeros((), dtype=query.dtype, device=query.device))
-        q_b = q_b.reshape(-1, heads_kv, rep, dim).float()
-        logits = torch.einsum("ngrd,xgd->ngrx", q_b, add_k[b].float()) * scale_value
-        lse_x = torch.logsumexp(logits, dim=-1)
-        out_x = torch.einsum("ngrx,xgd->ngrd", torch.softmax(logits, dim=-1), add_v[b].float())
-        outs.append(out_x.reshape(spatial + (heads_q, dim)).to(query.dtype))
-        lses.append(lse_x.reshape(spatial + (heads_q,)))
-    out_m, lse_m = _ag.merge_pair_with_grad(out, lse, torch.stack(outs), torch.stack(lses))
+    q_in = torch.where(mask[..., None, None], query, torch.zeros((), dtype=query.dtype, device=query.device))
+    q_in = q_in.reshape(batch, -1, heads_q, dim)
+    out_x, lse_x = _ag.dense_extra_with_grad(q_in, add_k, add_v, scale_value)   # head dim is 32, 64 or 128 here
+    out_x = out_x.reshape(query.shape)
+    lse_x = lse_x.reshape(query.shape[:-1])
+    out_m, lse_m = _ag.merge_pair_with_grad(out, lse, out_x, lse_x)
     keep = mask[..., None]
     return out_m * keep[..., None].to(out_m.dtype), lse_m * keep.to(lse_m.dtype)
 
