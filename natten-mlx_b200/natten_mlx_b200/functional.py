@@ -100,6 +100,15 @@ def _na(rank, query, key, value, kernel_size, stride, dilation, is_causal, scale
     if all(k >= e for k, e in zip(ks, spatial)) and all(s == 1 for s in st) and not any(ca):
         # kernel covers every axis: dense attention over the extent (functional.py:141-143, 271)
         ca = (2,) * rank
+    if add_k is not None and query.is_cuda and query.dtype in (torch.float16, torch.bfloat16) \
+            and query.shape[-1] in (32, 64, 128) and all(s == 1 for s in st):
+        # shapes the tensor-core kernels take: the neighbourhood branch runs there, the extra tokens
+        # as in the reference's composition (functional.py:340-381): dense attention + merge
+        out, lse = _ag.fused_with_grad(query, key, value, ks, st, dl, ca, scale_value)
+        q_flat = query.reshape(query.shape[0], -1, query.shape[-2], query.shape[-1])
+        out_x, lse_x = _ag.dense_extra_with_grad(q_flat, add_k, add_v, scale_value)
+        out, lse = _ag.merge_pair_with_grad(out, lse, out_x.reshape(out.shape), lse_x.reshape(lse.shape))
+        return (out, lse) if return_lse else out
     out, lse = _ag.fused_with_grad(query, key, value, ks, st, dl, ca, scale_value, add_k, add_v)
     return (out, lse) if return_lse else out
 

@@ -109,3 +109,32 @@ def test_mem_extent_is_refused_where_it_does_not_apply():
     assert lib.natten_b200_qk_forward(_lib.make_geom(1, 1, 2, 2, 32, _lib.BF16, [16], [3], [1], [1], [0], 1.0,
                                                      mem_extent=[32]), q.data_ptr(), q.data_ptr(), None, o.data_ptr(),
                                       None) == _lib.EINVAL
+
+
+@pytest.mark.parametrize("shape,hkv,ks,dl,ca,n_extra", [
+    ((2, 20, 24, 4, 64), 2, (7, 5), (1, 2), (False, False), 6),
+    ((1, 40, 2, 32), 2, (9,), (1,), (True,), 3),
+])
+def test_extra_tokens_composed_on_the_tensor_core_path(shape, hkv, ks, dl, ca, n_extra):
+    """Dense (not variable-size) call with extra tokens in bf16: neighbourhood branch on the tensor-core
+    kernels, extra tokens by dense attention, merged through the log-sum-exps; out, lse and all gradients
+    (including the one that flows through the returned lse) against the oracle."""
+    rank = len(shape) - 3
+    dt = torch.bfloat16
+    kv_shape = shape[:-2] + (hkv, shape[-1])
+    ins = [_rand(shape, 1, dt), _rand(kv_shape, 2, dt), _rand(kv_shape, 3, dt),
+           _rand((shape[0], n_extra, hkv, shape[-1]), 6, dt), _rand((shape[0], n_extra, hkv, shape[-1]), 7, dt)]
+    cot, cot_l = _rand(shape, 4, dt), _rand(shape[:-1], 5)
+    ref = lambda q, k, v, a, b: oracle.na(q, k, v, ks, 1, dl, ca, return_lse=True, additional_keys=a,
+                                          additional_values=b)
+    (o_ref, l_ref), g_ref = oracle.grads(ref, [t.float() for t in ins], (cot.float(), cot_l))
+    fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[rank]
+    dev_ins = [t.to(DEV).requires_grad_(True) for t in ins]
+    out, lse = fn(dev_ins[0], dev_ins[1], dev_ins[2], kernel_size=ks, dilation=dl, is_causal=ca, return_lse=True,
+                  additional_keys=dev_ins[3], additional_values=dev_ins[4])
+    assert _lib.last_path() == "tcgen05"
+    grads = torch.autograd.grad((out, lse), dev_ins, (cot.to(DEV), cot_l.to(DEV)))
+    _close(out, o_ref, "out")
+    _close(lse, l_ref, "lse")
+    for name, a, b in zip(("dq", "dk", "dv", "dak", "dav"), grads, g_ref):
+        _close(a, b, name)
