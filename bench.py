@@ -482,14 +482,102 @@ def run_table_workload(args):
         "roofline": roofline, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}))
 
 
+# ---------------------------------------------------------------------------
+# BASELINE config 4 sharded along T over the ranks (strong scaling, K/V halo exchange over NCCL)
+# ---------------------------------------------------------------------------
+def run_tshard(args, rank, world, local_rank):
+    import torch.distributed as dist
+    import natten_mlx_b200 as nb
+    from natten_mlx_b200 import _lib, sharding
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    w = WORKLOADS["na3d_video"]
+    B, T = w["shape"][0], w["shape"][1]
+    bounds = sharding.shard_bounds(T, world)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    gen = torch.Generator().manual_seed(1240 + rank)
+    local = (B, hi - lo) + tuple(w["shape"][2:])
+    q, k, v, cot = (torch.randn(local, generator=gen, dtype=torch.float32).to(torch.bfloat16).to(dev) for _ in range(4))
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+    ks, dl, ca = w["kernel"], w["dilations"][0], w["causal"]
+
+    def step():
+        if world == 1:
+            out = nb.na3d(q, k, v, kernel_size=ks, dilation=dl, is_causal=ca)
+        else:
+            out = sharding.na_sharded(q, k, v, T, ks, dl, ca)
+        return torch.autograd.grad(out, (q, k, v), cot)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for a, b in evs:
+        flush.zero_()
+        if world > 1:
+            dist.barrier()                    # every rank starts a step together: the halo exchange is inside it
+        a.record()
+        step()
+        b.record()
+    barrier()
+    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if rank != 0:
+        return
+    flops = flops_step(w)
+    print(json.dumps({
+        "metric": "na_fwd_bwd_effective_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["label"] + f", sharded along T over {world} rank(s), K/V halo planes by NCCL send/recv",
+                   "planes_per_rank": [bounds[r + 1] - bounds[r] for r in range(world)],
+                   "l2": "256 MiB buffer written between timed iterations", "kernel_family": _lib.last_path()},
+        "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="na2d_nat_stage", choices=sorted(WORKLOADS) + list(TABLE_WORKLOADS))
+    ap.add_argument("--workload", default="na2d_nat_stage",
+                    choices=sorted(WORKLOADS) + list(TABLE_WORKLOADS) + ["na3d_video_tshard"])
     args = ap.parse_args()
+    if args.workload == "na3d_video_tshard":
+        rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+        local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the sharded workload has no reference arm"}))
+            return
+        if world > 1:
+            import torch.distributed as dist
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        try:
+            run_tshard(args, rank, world, local_rank)
+        finally:
+            if world > 1:
+                import torch.distributed as dist
+                dist.destroy_process_group()
+        return
     if args.workload in TABLE_WORKLOADS:
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "table workloads have no reference arm"}))

@@ -60,7 +60,8 @@ struct FwdParams {
   int B, Hq, Hkv, rep, D;
   int rank;              // spatial rank of the tensors (tensor-map rank = rank + 2)
   int L[3], K[3], dl[3], ca[3];
-  int M[3];                           // extents behind the memory strides (== L for dense tensors)
+  int Mr[3], Mc[3];                   // extents behind the memory strides of the row / chunk tensors (== L when dense)
+  int ro0, re0, co0, ce0;             // leading-axis slab: first global plane and plane count of the row / chunk tensors
   int T[3];              // query tile extents in class coordinates
   int hpt, P;            // heads per tile, positions per tile (hpt * P == 128)
   int box[3];            // key box extents
@@ -108,6 +109,11 @@ size_t smem_needed(const FwdParams& p) {
   const size_t stats = p.mode == 2 ? (size_t)p.kv_stages * 2 * p.n_pad * 4 : 0;   // per-column lse / delta
   return 1024 /*alignment slack*/ + q + kv + stats + (size_t)kMaxWords * 128 * 4 + 2560 /*barriers, work items, window tables*/;
 }
+
+// Class entries i (global position i * d + g) of dilation class g that lie in planes [first, ...): the first one,
+// and for an exclusive end plane the one past the last.
+__host__ __device__ inline int slab_lo(int first, int g, int d) { return first <= g ? 0 : (first - g + d - 1) / d; }
+__host__ __device__ inline int slab_hi(int end, int g, int d) { return end <= g ? 0 : (end - g + d - 1) / d; }
 
 // Window of query i of a dilation class in class coordinates (the host twin of class_window()
 // in the kernels): valid keys are [max(s, 0), e).
@@ -157,6 +163,12 @@ int max_query_span(int L, int K, int d, int T) {
 long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
   int lgmax[3];
   for (int a = 0; a < 3; ++a) lgmax[a] = ceil_div(g.ge[a], g.dl[a]);
+  // row class entries on the leading axis that lie in the local slab (all of them when unsharded)
+  int nloc0 = 0;
+  for (int g0 = 0; g0 < g.dl[0]; ++g0) {
+    const int n = slab_hi(p.ro0 + p.re0, g0, g.dl[0]) - slab_lo(p.ro0, g0, g.dl[0]);
+    if (n > nloc0) nloc0 = n;
+  }
   long long best_cost = -1;
   int want[3] = {0, 0, 0};                       // tuning aid: pin the tile shape ("t0,t1,t2")
   if (const char* env_tile = getenv("NATTEN_B200_TILE")) sscanf(env_tile, "%d,%d,%d", &want[0], &want[1], &want[2]);
@@ -194,11 +206,11 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
       if (n_pad > 256) n_pad = (n_pad + 31) & ~31;
       if (n_pad > nmax) continue;
       long long tiles = 1;
-      for (int a = 0; a < 3; ++a) tiles *= ceil_div(lgmax[a], T[a]);
+      for (int a = 0; a < 3; ++a) tiles *= ceil_div(a == 0 ? nloc0 : lgmax[a], T[a]);
       const long long cost = tiles * nch * (n_pad + 96);      // +96: fixed per-chunk overhead
       if (best_cost < 0 || cost < best_cost) {
         best_cost = cost;
-        for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(lgmax[a], T[a]); }
+        for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(a == 0 ? nloc0 : lgmax[a], T[a]); }
         p.chunk_axis = ca; p.R = R; p.cchunks = cch; p.n_chunks = nch; p.inner = inner;
         p.n_cols = R * inner; p.n_pad = n_pad; p.rp = rp;
       }
@@ -218,12 +230,28 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode) {
   int ncls = 1;
   for (int a = 0; a < 3; ++a) {
     if (g.st[a] != 1) { pl.why = "stride > 1"; return pl; }
-    if (g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a] || g.qo[a] != 0 || g.ko[a] != 0) { pl.why = "sharded slab"; return pl; }
+    if ((g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a] || g.qo[a] != 0 || g.ko[a] != 0) && (a != 0 || g.rank != 3)) {
+      pl.why = "slab on an axis other than the leading axis of a 3-D volume";
+      return pl;
+    }
     ncls *= g.dl[a];
   }
   if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
   base.B = g.B; base.Hq = g.Hq; base.Hkv = g.Hkv; base.rep = g.rep; base.D = g.D; base.rank = g.rank;
-  for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.M[a] = g.me[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
+  for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
+  {
+    // rows are queries (forward, dQ) or keys (dK/dV); the chunk operands are the other side
+    const bool rows_are_q = mode != 2;
+    const bool slab = g.qe[0] != g.ge[0] || g.ke[0] != g.ge[0];
+    for (int a = 0; a < 3; ++a) {
+      base.Mr[a] = slab ? (rows_are_q ? g.qe[a] : g.ke[a]) : g.me[a];
+      base.Mc[a] = slab ? (rows_are_q ? g.ke[a] : g.qe[a]) : g.me[a];
+    }
+    base.ro0 = rows_are_q ? g.qo[0] : g.ko[0];
+    base.re0 = rows_are_q ? g.qe[0] : g.ke[0];
+    base.co0 = rows_are_q ? g.ko[0] : g.qo[0];
+    base.ce0 = rows_are_q ? g.ke[0] : g.qe[0];
+  }
   base.mode = mode;
   base.hpt = mode == 2 ? 1 : ((g.rep % 4 == 0) ? 4 : (g.rep % 2 == 0 ? 2 : 1));
   base.head_groups = mode == 2 ? 1 : g.rep / base.hpt;
@@ -355,14 +383,18 @@ EncodeTiledFn encode_fn() {
 // One map per dilation class for a [B, spatial..., heads, D] tensor.
 // dims: (heads*D, axis rank-1, ..., axis 0, B); box_sp[a] is the box extent on
 // normalised axis a (leading trivial axes of lower-rank tensors are skipped).
-int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, int heads, const int box_sp[3]) {
+// `chunk_side`: the tensor is a chunk operand (its own slab range and strides) rather than a row operand.
+int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, int heads, const int box_sp[3],
+                      bool chunk_side = false) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return set_error(NATTEN_B200_ENODEVICE, "cuTensorMapEncodeTiled is not available");
   const int lead = 3 - p.rank;
   const cuuint32_t trank = (cuuint32_t)(p.rank + 2);
+  const int* ext = chunk_side ? p.Mc : p.Mr;
+  const int first0 = chunk_side ? p.co0 : p.ro0, count0 = chunk_side ? p.ce0 : p.re0;
   long long stride_el[3];  // elements between consecutive coordinates on each axis
   long long s = (long long)heads * p.D;
-  for (int a = 2; a >= 0; --a) { stride_el[a] = s; s *= p.M[a]; }
+  for (int a = 2; a >= 0; --a) { stride_el[a] = s; s *= ext[a]; }
   const long long batch_el = s;
   int ci = 0;
   for (int g0 = 0; g0 < p.dl[0]; ++g0)
@@ -377,10 +409,18 @@ int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, i
         box[0] = (cuuint32_t)p.dblk;
         int di = 1;
         for (int a = 2; a >= lead; --a, ++di) {
-          dims[di] = (cuuint64_t)ceil_div(p.L[a] - gcls[a], p.dl[a]);
+          long long n = ceil_div(p.L[a] - gcls[a], p.dl[a]);
+          long long first_plane = gcls[a];              // local plane of the class's first entry
+          if (a == 0) {                                 // leading axis: only the entries inside the local planes
+            const int lo = slab_lo(first0, g0, p.dl[0]), hi = slab_hi(first0 + count0, g0, p.dl[0]);
+            n = hi - lo;
+            first_plane = (long long)lo * p.dl[0] + g0 - first0;
+            if (n <= 0) { n = 1; first_plane = 0; }     // a class without local entries: its tiles are dead
+          }
+          dims[di] = (cuuint64_t)n;
           strides[di - 1] = (cuuint64_t)(stride_el[a] * p.dl[a] * 2);
           box[di] = (cuuint32_t)box_sp[a];
-          off += gcls[a] * stride_el[a];
+          off += first_plane * stride_el[a];
         }
         dims[di] = (cuuint64_t)p.B;
         strides[di - 1] = (cuuint64_t)(batch_el * 2);

@@ -103,3 +103,36 @@ def test_tcgen05_backward(dtype, shape, hkv, ks, dl, ca):
     dq2, dk2, dv2, _, _ = backend.fused_backward(qd, kd, vd, out, lse, cot.to(DEV), cot_l.to(DEV), ks, one, dl, ca,
                                                  None, path="tcgen05")
     assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+
+
+@pytest.mark.parametrize("shape,ks,dl,ca,world", [
+    ((1, 12, 9, 10, 2, 32), (3, 3, 5), (2, 1, 1), (True, False, False), 2),
+    ((1, 12, 9, 10, 2, 32), (3, 3, 5), (2, 1, 1), (False, False, False), 2),
+    ((2, 16, 12, 16, 4, 64), (5, 7, 3), (1, 1, 2), (False, False, False), 3),
+    ((1, 20, 8, 8, 2, 32), (3, 3, 3), (3, 1, 1), (True, False, False), 4),
+])
+def test_leading_axis_slabs_on_the_tensor_core_kernels(shape, ks, dl, ca, world):
+    """Slabs of a 3-D volume along its leading axis (K/V with halo planes, windows in global
+    coordinates): out and dq of every slab, and dk/dv with the halo partials added, equal the
+    unsharded result of the same kernels."""
+    from natten_mlx_b200.sharding import fused_slab_forward_backward, slab_plan
+    dt = torch.bfloat16
+    q, k, v, cot = (_rand(shape, 100 + i, dt).to(DEV) for i in range(4))
+    one = (1, 1, 1)
+    o_ref, lse_ref = backend.fused_forward(q, k, v, ks, one, dl, ca, None, path="tcgen05")
+    g_ref = backend.fused_backward(q, k, v, o_ref, lse_ref, cot, None, ks, one, dl, ca, None, path="tcgen05")
+    T = shape[1]
+    dk_full, dv_full = torch.zeros_like(k, dtype=torch.float32), torch.zeros_like(v, dtype=torch.float32)
+    for r in range(world):
+        plan = slab_plan(T, world, r, ks[0], dl[0], ca[0])
+        o, lse, dq, dk_, dv_ = fused_slab_forward_backward(
+            q[:, plan.q_lo:plan.q_hi], k[:, plan.kv_lo:plan.kv_hi], v[:, plan.kv_lo:plan.kv_hi],
+            cot[:, plan.q_lo:plan.q_hi], plan, shape[1:4], ks, dl, ca, None)
+        assert _lib.last_path() == "tcgen05" and _lib.kernel_status() == 0
+        assert _rel(o, o_ref[:, plan.q_lo:plan.q_hi]) < 1e-2            # tiles differ, so rounding may
+        assert _rel(lse, lse_ref[:, plan.q_lo:plan.q_hi]) < 1e-3
+        assert _rel(dq, g_ref[0][:, plan.q_lo:plan.q_hi]) < 1e-2
+        dk_full[:, plan.kv_lo:plan.kv_hi] += dk_.float()
+        dv_full[:, plan.kv_lo:plan.kv_hi] += dv_.float()
+    assert _rel(dk_full, g_ref[1]) < 2e-2
+    assert _rel(dv_full, g_ref[2]) < 2e-2
