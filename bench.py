@@ -302,6 +302,11 @@ def run_ours(args, w, rank, world, local_rank):
             ms = float(t.item())
         return ms / steps
 
+    # measured tiling per variant (the library's tuning entry point; part of the warm-up, recorded in `config`)
+    tuned = {}
+    for (q, k, v, cot), dil in zip(dev_in, w["dilations"]):
+        res = nb.tune.tune_fused(q, k, v, w["kernel"], dilation=dil, is_causal=w["causal"])
+        tuned["x".join(str(d) for d in dil)] = {kn: {"tile": list(t), "max_cols": c} for kn, (t, c, _) in res.items()}
     for _ in range(max(args.warmup, 3)):
         step_device()
     sampler = ClockSampler(local_rank)
@@ -363,7 +368,8 @@ def run_ours(args, w, rank, world, local_rank):
                    "global_batch": w["shape"][0] * world, "parallelism": f"batch-sharded x{world}, no collective",
                    "l2": "256 MiB buffer written between timed iterations; separate inputs per variant",
                    "kernel_family": path, "flops_model": "fwd 4*B*H*N*K_vol*D, bwd 2.5x fwd",
-                   "ms_per_call_fwd_bwd": ms_plain / nvar},
+                   "ms_per_call_fwd_bwd": ms_plain / nvar,
+                   "tuned_plans": tuned},
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},

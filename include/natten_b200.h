@@ -210,6 +210,15 @@ void natten_b200_debug_set_s_dump(float* device_buffer);
  * place of the reference's tuning tables (src/natten_mlx/_core/_forward_tuning.py:11-34). */
 int natten_b200_describe_plan(const natten_b200_geom* g, char* buf, size_t cap);
 
+/* Pins the tiling of one geometry for one tensor-core kernel (kernel: 0 forward, 1 dQ, 2 dK/dV):
+ * tile = query/key tile extents per axis (rank entries, product = 128 / packed heads; NULL or
+ * zeros = planner's choice) and max_cols = cap on the chunk width in S columns (0 = none).  The
+ * hint stays until it is replaced; zeros release it.  NATTEN_B200_EINVAL when no plan exists with
+ * the hint (the hint is then dropped).  This is the write side of the reference's tuning tables
+ * (src/natten_mlx/_core/_forward_tuning.py:11-34, _softmax_tuning.py): a caller that measures
+ * candidates on its own shapes (natten_mlx_b200.tune.tune_fused does) records the winner here. */
+int natten_b200_plan_hint(const natten_b200_geom* g, int32_t kernel, const int32_t* tile, int32_t max_cols);
+
 /* Bytes of scratch natten_b200_fused_backward needs for this geometry. */
 size_t natten_b200_fused_backward_scratch_bytes(const natten_b200_geom* g);
 

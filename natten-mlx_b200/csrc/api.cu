@@ -358,6 +358,17 @@ int natten_b200_kernel_status(void) { return sm100_read_status(); }
 
 void natten_b200_debug_set_s_dump(float* device_buffer) { sm100_set_debug_s(device_buffer); }
 
+int natten_b200_plan_hint(const natten_b200_geom* gi, int32_t kernel, const int32_t* tile, int32_t max_cols) {
+  Geo g;
+  if (int rc = make_geo(gi, &g)) return rc;
+  if (kernel < 0 || kernel > 2) return set_error(NATTEN_B200_EINVAL, "plan_hint: kernel must be 0 (forward), 1 (dQ) or 2 (dK/dV)");
+  const int none[3] = {0, 0, 0};
+  int t3[3] = {1, 1, 1};
+  if (tile != nullptr)
+    for (int i = 0; i < gi->rank; ++i) t3[3 - gi->rank + i] = tile[i];
+  return sm100_plan_hint(g, gi->dtype, kernel, tile != nullptr ? t3 : none, max_cols);
+}
+
 int natten_b200_describe_plan(const natten_b200_geom* gi, char* buf, size_t cap) {
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;

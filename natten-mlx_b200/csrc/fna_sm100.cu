@@ -160,7 +160,13 @@ int max_query_span(int L, int K, int d, int T) {
 
 // Best query tile for a cap of `nmax` S columns per chunk; returns the cost
 // (tiles x chunks x padded columns) or -1 when nothing fits.
-long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
+// A pinned tile shape and chunk-width cap for one geometry and kernel (plan_hint entry point); zeros pin nothing.
+struct PlanHint {
+  int tile[3];
+  int max_cols;
+};
+
+long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const PlanHint& hint) {
   int lgmax[3];
   for (int a = 0; a < 3; ++a) lgmax[a] = ceil_div(g.ge[a], g.dl[a]);
   // row class entries on the leading axis that lie in the local slab (all of them when unsharded)
@@ -172,6 +178,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
   long long best_cost = -1;
   int want[3] = {0, 0, 0};                       // tuning aid: pin the tile shape ("t0,t1,t2")
   if (const char* env_tile = getenv("NATTEN_B200_TILE")) sscanf(env_tile, "%d,%d,%d", &want[0], &want[1], &want[2]);
+  if (hint.tile[2] > 0) { want[0] = hint.tile[0]; want[1] = hint.tile[1]; want[2] = hint.tile[2]; }
   for (int t2 = 1; t2 <= p.P; t2 *= 2)
     for (int t1 = 1; t1 * t2 <= p.P; t1 *= 2) {
       const int t0 = p.P / (t1 * t2);
@@ -218,7 +225,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode) {
   return best_cost;
 }
 
-Plan make_plan_uncached(const Geo& g, int dtype, int mode) {
+Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint) {
   Plan pl{};
   pl.ok = false;
   FwdParams base{};
@@ -269,7 +276,7 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode) {
   const char* force = getenv("NATTEN_B200_CTAS_PER_SM");   // tuning aid: pin the CTAs per SM
   const int forced = force != nullptr ? atoi(force) : 0;
   const char* env_cols = getenv("NATTEN_B200_MAX_COLS");   // tuning aids: cap the chunk width / ring depth
-  const int max_cols = env_cols != nullptr ? atoi(env_cols) : 0;
+  const int max_cols = hint.max_cols > 0 ? hint.max_cols : (env_cols != nullptr ? atoi(env_cols) : 0);
   const char* env_sbuf = getenv("NATTEN_B200_MAX_SBUF");
   const int max_sbuf = env_sbuf != nullptr ? atoi(env_sbuf) : 0;
   const char* env_minsb = getenv("NATTEN_B200_MIN_SBUF");
@@ -292,7 +299,7 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode) {
         const int s_regions = mode == 0 ? nb : 2 * nb;
         if (cap * s_regions > tmem_cols - acc_cols) continue;
         FwdParams p = base;
-        const long long cost = choose_tile(g, p, cap, mode);
+        const long long cost = choose_tile(g, p, cap, mode, hint);
         if (cost < 0) continue;
         p.q_stages = 2; p.kv_stages = 4; p.n_sbuf = nb;   // backward: up to four chunk-operand stages
         if (mode == 0) {
@@ -337,25 +344,55 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode) {
 
 // Plans depend on the geometry only; building one walks tile shapes, chunk widths and (for the
 // dK/dV kernel) every key tile of every axis, which costs the host far more than a launch.
-Plan make_plan(const Geo& g, int dtype, int mode = 0) {
-  static const bool tuning = getenv("NATTEN_B200_CTAS_PER_SM") || getenv("NATTEN_B200_MAX_COLS") ||
-                             getenv("NATTEN_B200_MAX_SBUF") || getenv("NATTEN_B200_MIN_SBUF") || getenv("NATTEN_B200_TILE");
-  if (tuning) return make_plan_uncached(g, dtype, mode);
+std::vector<int> plan_key(const Geo& g, int dtype, int mode) {
   std::vector<int> key = {dtype, mode, g.B, g.Hq, g.Hkv, g.D, g.rank, g.n_extra, g.extents != nullptr ? 1 : 0};
   int scale_bits;
   memcpy(&scale_bits, &g.scale, sizeof(int));
   key.push_back(scale_bits);
   for (int a = 0; a < 3; ++a)
     for (int v : {g.qe[a], g.ke[a], g.ge[a], g.me[a], g.qo[a], g.ko[a], g.K[a], g.st[a], g.dl[a], g.ca[a]}) key.push_back(v);
-  static std::mutex mu;
-  static std::map<std::vector<int>, Plan> cache;
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(key);
-  if (it != cache.end()) return it->second;
-  if (cache.size() > 4096) cache.clear();          // many distinct per-sample sizes: start over rather than grow
-  const Plan pl = make_plan_uncached(g, dtype, mode);
-  cache.emplace(std::move(key), pl);
+  return key;
+}
+
+std::mutex g_plan_mu;
+std::map<std::vector<int>, Plan> g_plan_cache;
+std::map<std::vector<int>, PlanHint> g_plan_hints;
+
+Plan make_plan(const Geo& g, int dtype, int mode = 0) {
+  static const bool tuning = getenv("NATTEN_B200_CTAS_PER_SM") || getenv("NATTEN_B200_MAX_COLS") ||
+                             getenv("NATTEN_B200_MAX_SBUF") || getenv("NATTEN_B200_MIN_SBUF") || getenv("NATTEN_B200_TILE");
+  std::vector<int> key = plan_key(g, dtype, mode);
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  PlanHint hint{{0, 0, 0}, 0};
+  auto h = g_plan_hints.find(key);
+  if (h != g_plan_hints.end()) hint = h->second;
+  if (tuning) return make_plan_uncached(g, dtype, mode, hint);
+  auto it = g_plan_cache.find(key);
+  if (it != g_plan_cache.end()) return it->second;
+  if (g_plan_cache.size() > 4096) g_plan_cache.clear();   // many distinct per-sample sizes: start over rather than grow
+  const Plan pl = make_plan_uncached(g, dtype, mode, hint);
+  g_plan_cache.emplace(std::move(key), pl);
   return pl;
+}
+
+// Pins (or with zeros releases) the tile shape and chunk-width cap of one geometry and kernel.
+int plan_hint_impl(const Geo& g, int dtype, int mode, const int tile[3], int max_cols) {
+  const std::vector<int> key = plan_key(g, dtype, mode);
+  PlanHint hint{{tile[0], tile[1], tile[2]}, max_cols};
+  {
+    std::lock_guard<std::mutex> lock(g_plan_mu);
+    if (hint.tile[2] <= 0 && hint.max_cols <= 0) g_plan_hints.erase(key);
+    else g_plan_hints[key] = hint;
+    g_plan_cache.erase(key);
+  }
+  const Plan pl = make_plan(g, dtype, mode);
+  if (!pl.ok) {
+    std::lock_guard<std::mutex> lock(g_plan_mu);
+    g_plan_hints.erase(key);
+    g_plan_cache.erase(key);
+    return set_error(NATTEN_B200_EINVAL, "plan_hint: no plan with this tile shape and chunk width: %s", pl.why);
+  }
+  return NATTEN_B200_OK;
 }
 
 // ---------------------------------------------------------------------------

@@ -23,5 +23,6 @@ void sm100_set_debug_s(float* ptr);
 // Text description of the tiling chosen for a geometry (no GPU needed).
 // mode: 0 forward, 1 dQ kernel, 2 dK/dV kernel.
 int sm100_describe_plan(const Geo& g, int dtype, int mode, char* buf, size_t cap);
+int sm100_plan_hint(const Geo& g, int dtype, int mode, const int tile[3], int max_cols);
 
 }  // namespace nb

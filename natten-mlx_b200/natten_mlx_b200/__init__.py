@@ -9,7 +9,7 @@ from ._core.cuda import get_fused_path, set_fused_path
 from .functional import (na1d, na1d_av, na1d_qk, na1d_varlen, na2d, na2d_av, na2d_qk, na2d_varlen, na3d,
                          na3d_av, na3d_qk, na3d_varlen)
 from .merge import merge_attentions
-from . import compat, host, nn  # noqa: E402  (callers of the operators: modules, old call conventions, host-resident tensors)
+from . import compat, host, nn, tune  # noqa: E402  (callers of the operators: modules, old call conventions, host-resident tensors)
 
 __version__ = "0.1.0"
 
@@ -29,7 +29,7 @@ def set_backend(name: str) -> None:
 
 __all__ = [
     "__version__", "get_backend", "set_backend", "has_cuda", "get_fused_path", "set_fused_path",
-    "merge_attentions", "nn", "compat", "host",
+    "merge_attentions", "nn", "compat", "host", "tune",
     "na1d", "na1d_av", "na1d_qk", "na1d_varlen",
     "na2d", "na2d_av", "na2d_qk", "na2d_varlen",
     "na3d", "na3d_av", "na3d_qk", "na3d_varlen",
