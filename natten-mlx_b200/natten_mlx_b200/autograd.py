@@ -90,13 +90,13 @@ class _DenseExtra(torch.autograd.Function):
         max_q, max_k, scale, rep = ctx.meta
         op_f = torch.ops.aten._scaled_dot_product_flash_attention
         op_b = torch.ops.aten._scaled_dot_product_flash_attention_backward
-        go = torch.zeros_like(out) if grad_out is None else grad_out.transpose(1, 2).contiguous()
+        go = torch.zeros_like(out) if grad_out is None else grad_out.transpose(1, 2)   # strided view: no copy
         dq, dk, dv = op_b(go, qt, kk, vv, out, lse, cq, ck, max_q, max_k, 0.0, False, seed, offset, scale=scale)
         if grad_lse is not None:
-            gl = (grad_lse.transpose(1, 2).to(torch.float32) * scale)[..., None]      # [B, Hq, N, 1]
+            gl = (grad_lse.transpose(1, 2) * scale).to(qt.dtype)[..., None]           # [B, Hq, N, 1]
             res = op_f(qt, kk, kk, 0.0, False, False, scale=scale)
-            dq = dq + (gl * res[0].float()).to(dq.dtype)
-            _, _, dk_l = op_b((gl * qt.float()).to(qt.dtype), qt, kk, kk, res[0], res[1], res[2], res[3], res[4], res[5],
+            dq.addcmul_(gl, res[0])
+            _, _, dk_l = op_b(gl * qt, qt, kk, kk, res[0], res[1], res[2], res[3], res[4], res[5],
                               0.0, False, res[6], res[7], scale=scale)
             dk = dk + dk_l
         b, hq, x, d = dk.shape
