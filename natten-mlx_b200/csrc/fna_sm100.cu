@@ -1,19 +1,19 @@
 // Tensor-core fused neighborhood attention, forward pass, for sm_100a.
 //
-// A CTA owns one (batch, kv head, dilation class, query tile).  Dilation is
-// removed up front: the queries p = i*d + g of one residue class g attend only
-// to keys of the same class, so each class is a dilation-1 problem on a
-// strided view and gets its own TMA tensor maps.  The 128 rows of the tile
-// are (heads sharing the kv head) x (tile positions).  The keys every row of
-// the tile can address form a box; the box is walked in chunks of at most a
-// few hundred keys.  Per chunk:
-//   TMA warp     K/V chunk -> shared memory (zero fill outside the tensor)
-//   MMA warp     S = Q K^T   (tcgen05.mma, operands in smem, S in TMEM)
-//   4 softmax warps   S -> registers, per-row window/causal mask from a
-//                bitmap, online softmax in base 2, P (bf16/f16) -> TMEM over S
-//   MMA warp     O += P V    (A = P from TMEM, B = V as an MN-major operand)
-// and at the end of the tile the softmax warps scale O by 1/l and write
-// out and the log-sum-exp.  Math as in src/natten_mlx/_core/pure.py:155-255
+// A persistent CTA walks (batch, kv head, head group, dilation class, query tile) work items.
+// Dilation is removed up front: the queries p = i*d + g of one residue class g attend only
+// to keys of the same class, so each class is a dilation-1 problem on a strided view and gets
+// its own TMA tensor maps.  The 128 rows of a tile are (heads sharing the kv head) x (tile
+// positions).  The keys every row of the tile can address form a box; the box is walked in
+// chunks (ranges of box rows), and the chunks of all tiles of a CTA form one stream:
+//   TMA warp     K/V chunks -> a ring of shared-memory stages (zero fill outside the tensor)
+//   MMA warp     S = Q K^T of chunk j+1 (tcgen05.mma, operands in smem, S in a ring of TMEM
+//                buffers), then O += P V of chunk j (A = P from TMEM, B = V MN-major)
+//   4 softmax warps   S -> registers over the box rows the warp needs, window/causal mask as
+//                additive offsets (or a bitmap for boxes without row structure), softmax in
+//                base 2 against a lazily updated reference maximum, P (bf16/f16) -> TMEM over S
+// and one chunk into the next tile the softmax warps scale the finished O by 1/l and write out
+// and the log-sum-exp.  Math as in src/natten_mlx/_core/pure.py:155-255
 // with the LSE of src/natten_mlx/functional.py:368-372.
 #include <cuda.h>
 #include <math.h>
@@ -37,7 +37,6 @@ using namespace sm100;
 constexpr int kMaxClasses = 16;
 constexpr int kTileM = 128;
 constexpr int kMaxCols = 384;            // S columns per chunk
-constexpr int kMaxGroups = kMaxCols / 16;
 constexpr int kMaxWords = kMaxCols / 32;
 constexpr int kThreads = 192;            // 4 softmax warps, 1 TMA warp, 1 MMA warp
 
@@ -69,7 +68,7 @@ struct FwdParams {
   int chunk_axis, R, cchunks, n_chunks, inner, n_cols, n_pad, n_split, n_half;
   int dblk, ndblk, row_bytes, layout_type;
   int q_stages, kv_stages;
-  int n_sbuf;                         // forward: depth of the S/P ring in tensor memory
+  int n_sbuf;                         // depth of the S/P (forward) or S+dP (backward) ring in tensor memory
   int ctas_per_sm, tmem_cols, ocol;   // TMEM: S/P at column 0, O at ocol
   // backward kernels: mode 1 = dQ (rows are queries), mode 2 = dK/dV (rows are keys)
   int mode, head_groups;
