@@ -157,6 +157,38 @@ int max_query_span(int L, int K, int d, int T) {
   return best;
 }
 
+// Mean over the tiles of one axis of (box rows some row of the tile needs) / (box rows): tiles at
+// the ends of an axis need fewer than the box holds, and the elementwise warps skip the rest.
+// Rows are queries and the box holds keys (rows_are_q), or the other way round.  Class 0 stands
+// for all dilation classes.
+double mean_needed_fraction(int L, int K, int d, int T, int box, bool rows_are_q) {
+  const int lg = (L + d - 1) / d;
+  std::vector<int> lo(lg), hi(lg);
+  for (int x = 0; x < lg; ++x) { lo[x] = lg; hi[x] = 0; }
+  for (int q = 0; q < lg; ++q) {
+    int s, e;
+    host_class_window(q, 0, lg, L, K, d, s, e);
+    if (s < 0) s = 0;
+    if (rows_are_q) { lo[q] = s; hi[q] = e; continue; }
+    for (int x = s; x < e; ++x) {
+      if (q < lo[x]) lo[x] = q;
+      if (q + 1 > hi[x]) hi[x] = q + 1;
+    }
+  }
+  double sum = 0.0;
+  int n = 0;
+  for (int t = 0; t < lg; t += T, ++n) {
+    int a = lg, b = 0;
+    for (int x = t; x < t + T && x < lg; ++x) {
+      if (lo[x] < a) a = lo[x];
+      if (hi[x] > b) b = hi[x];
+    }
+    const int need = b - a < box ? b - a : box;
+    sum += (double)(need > 0 ? need : 0) / box;
+  }
+  return n > 0 ? sum / n : 1.0;
+}
+
 // Best query tile for a cap of `nmax` S columns per chunk; returns the cost
 // (tiles x chunks x padded columns) or -1 when nothing fits.
 // A pinned tile shape and chunk-width cap for one geometry and kernel (plan_hint entry point); zeros pin nothing.
@@ -175,6 +207,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
     if (n > nloc0) nloc0 = n;
   }
   long long best_cost = -1;
+  double best_visited = 1.0;
   int want[3] = {0, 0, 0};                       // tuning aid: pin the tile shape ("t0,t1,t2")
   if (const char* env_tile = getenv("NATTEN_B200_TILE")) sscanf(env_tile, "%d,%d,%d", &want[0], &want[1], &want[2]);
   if (hint.tile[2] > 0) { want[0] = hint.tile[0]; want[1] = hint.tile[1]; want[2] = hint.tile[2]; }
@@ -213,9 +246,16 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
       if (n_pad > nmax) continue;
       long long tiles = 1;
       for (int a = 0; a < 3; ++a) tiles *= ceil_div(a == 0 ? nloc0 : lgmax[a], T[a]);
+      // box rows (axes 0 and 1) that no row of a tile needs are skipped by the elementwise warps:
+      // among tile shapes of equal cost the one with the fewest visited rows wins
+      double visited = 1.0;
+      for (int a = 0; a < 2; ++a)
+        if (g.ge[a] > 1 && g.ca[a] == 0 && box[a] > 1)
+          visited *= mean_needed_fraction(g.ge[a], g.K[a], g.dl[a], T[a], box[a], mode != 2);
       const long long cost = tiles * nch * (n_pad + 96);      // +96: fixed per-chunk overhead
-      if (best_cost < 0 || cost < best_cost) {
+      if (best_cost < 0 || cost < best_cost || (cost == best_cost && visited < best_visited - 1e-9)) {
         best_cost = cost;
+        best_visited = visited;
         for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(a == 0 ? nloc0 : lgmax[a], T[a]); }
         p.chunk_axis = ca; p.R = R; p.cchunks = cch; p.n_chunks = nch; p.inner = inner;
         p.n_cols = R * inner; p.n_pad = n_pad; p.rp = rp;

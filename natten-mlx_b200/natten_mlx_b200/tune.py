@@ -32,7 +32,7 @@ def _tile_shapes(rank: int, rows: int):
 
 
 def tune_fused(query, key, value, kernel_size, dilation=1, is_causal=False, scale: Optional[float] = None,
-               max_cols: Sequence[int] = (0, 128, 96, 80, 64, 48), repeats: int = 3, verbose: bool = False
+               max_cols: Sequence[int] = (0, 256, 192, 128, 96, 80, 64, 48), repeats: int = 3, verbose: bool = False
                ) -> Dict[str, Tuple[Tuple[int, ...], int, float]]:
     """Times candidate tilings of the fused forward and backward for these tensors and pins the best.
 
