@@ -73,13 +73,19 @@ constexpr uint32_t kPollLimit = 2048;  // probes before a wait on the critical p
 
 // Waits for the phase with the given parity.  Returns false when the CTA is
 // aborting (this wait ran out, or another one did before).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// The retry loop exists once per kernel (it is reached only when the first probe fails, and a
+// dozen inlined copies of it would only take room in the instruction cache).
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag);
 }
 
 // The same for the waits between the MMA thread and the warps that feed it: a sleeping
