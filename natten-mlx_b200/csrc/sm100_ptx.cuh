@@ -92,6 +92,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // thread takes a few hundred cycles to wake, so the phase is polled first (a bounded number
 // of probes) and the sleeping wait takes over only when the phase is far away.
 __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
   for (uint32_t it = 0; it < kPollLimit; ++it)
     if (mbar_test_wait(bar, parity)) return true;
   return mbar_wait(bar, parity, abort_flag);
