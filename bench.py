@@ -529,6 +529,8 @@ def run_tshard(args, rank, world, local_rank):
     launches0 = _lib.launch_count()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
+    _lib.trace_report()
+    _lib.trace_enable(True)                   # per-kernel device times of this rank (events around each launch)
     for a, b in evs:
         flush.zero_()
         if world > 1:
@@ -537,6 +539,8 @@ def run_tshard(args, rank, world, local_rank):
         step()
         b.record()
     barrier()
+    _lib.trace_enable(False)
+    kernels = {k: {"launches": n, "ms_per_launch": t / n} for k, (n, t) in sorted(_lib.trace_report().items())}
     ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -554,7 +558,8 @@ def run_tshard(args, rank, world, local_rank):
         "config": {"workload": w["label"] + f", sharded along T over {world} rank(s), K/V halo planes by NCCL send/recv",
                    "planes_per_rank": [bounds[r + 1] - bounds[r] for r in range(world)],
                    "l2": "256 MiB buffer written between timed iterations", "kernel_family": _lib.last_path()},
-        "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}))
+        "roofline": None, "kernels_rank0": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches),
+        "clocks": clocks}))
 
 
 def main():
