@@ -168,3 +168,21 @@ def test_validation_errors():
     with pytest.raises(ValueError, match="kernel volume|kernel area|neighborhood dimension"):
         from natten_mlx_b200._core import cuda
         cuda._check_attn(torch.randn(1, 16, 2, 4), q, 1, (3,), (1,))
+
+
+def test_planner_is_host_only_and_breaks_ties_by_needed_rows():
+    """The tiling plan is worked out on the host (no GPU needed to describe it).  At dilation 4 a
+    56x56 image has 14x14 positions per dilation class: a 16x8 and an 8x16 key tile cost the same
+    padded columns, but the queries that address an 8-row key tile span fewer box rows, and the
+    elementwise warps skip the rows nobody needs, so the planner takes 8x16 for dK/dV."""
+    g = _lib.make_geom(2, 32, 4, 4, 32, _lib.BF16, (56, 56), (7, 7), (1, 1), (4, 4), [0, 0], 32 ** -0.5)
+    parts = _lib.describe_plan(g).split(" | ")
+    assert len(parts) == 3 and all("unsupported" not in p for p in parts)
+    assert "tile 1x8x16" in parts[2] and "box 1x14x16" in parts[2]
+    # dilation 1: the key box of a 16x8 query tile is 22 rows of 14 -> 16 padded columns
+    g1 = _lib.make_geom(2, 32, 4, 4, 32, _lib.BF16, (56, 56), (7, 7), (1, 1), (1, 1), [0, 0], 32 ** -0.5)
+    fwd = _lib.describe_plan(g1).split(" | ")[0]
+    assert "tile 1x16x8" in fwd and "box 1x22x16" in fwd and "2 CTA/SM" in fwd
+    # a shape the tensor-core kernels do not take says why
+    gbad = _lib.make_geom(1, 4, 8, 8, 64, _lib.BF16, (8192,), (127,), (1,), (1,), [0], 64 ** -0.5)
+    assert "unsupported" in _lib.describe_plan(gbad)
