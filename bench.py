@@ -106,7 +106,7 @@ def algorithmic_bytes(w):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from an ncu capture of one forward+backward call of
 # the default workload; workloads without a capture report null.
-NCU_TRAFFIC = {"na2d_nat_stage": {"fna_fwd_sm100": 85.3e6, "fna_bwd_dq_sm100": 117.6e6, "fna_bwd_dkv_sm100": 130.6e6,
+NCU_TRAFFIC = {"na2d_nat_stage": {"fna_fwd_sm100": 83.9e6, "fna_bwd_dq_sm100": 117.6e6, "fna_bwd_dkv_sm100": 130.6e6,
                                   "fna_bwd_prep_sm100": 51.4e6}}
 
 
