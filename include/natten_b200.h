@@ -200,10 +200,6 @@ int natten_b200_fused_forward(const natten_b200_geom* g, const void* q, const vo
  */
 int natten_b200_kernel_status(void);
 
-/* Diagnostic for tests: when device_buffer is not NULL the tensor-core forward
- * writes the raw QK^T tile of its first work item there
- * ([chunks][128][padded columns] float32).  No counterpart in the reference. */
-void natten_b200_debug_set_s_dump(float* device_buffer);
 
 /* Writes a one-line description of the tensor-core tiling chosen for a
  * geometry (or why it is unsupported) into buf.  Needs no GPU.  Takes the

@@ -179,6 +179,17 @@ static bool any_null(std::initializer_list<const void*> ptrs) {
   return false;
 }
 
+// The kernels read and write rows through 16-byte vector accesses and TMA tensor maps, both of
+// which need 16-byte aligned base addresses (null pointers of optional tensors pass).
+static bool any_misaligned(std::initializer_list<const void*> ptrs) {
+  for (const void* p : ptrs)
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return true;
+  return false;
+}
+static int reject_misaligned(const char* what) {
+  return set_error(NATTEN_B200_EINVAL, "%s: tensor pointers must be 16-byte aligned", what);
+}
+
 }  // namespace nb
 
 using namespace nb;
@@ -253,6 +264,7 @@ int natten_b200_qk_forward(const natten_b200_geom* gi, const void* q, const void
   if (int rc = make_geo(gi, &g)) return rc;
   if (int rc = reject_pitched(g, "qk_forward")) return rc;
   if (any_null({q, k, logits})) return set_error(NATTEN_B200_EINVAL, "qk_forward: null tensor");
+  if (any_misaligned({q, k, logits})) return reject_misaligned("qk_forward");
   if (bias != nullptr) {
     for (int a = 0; a < 3; ++a)
       if (g.st[a] != 1 || g.ca[a]) return set_error(NATTEN_B200_EINVAL, "bias requires stride 1 and no causal axis");
@@ -266,6 +278,7 @@ int natten_b200_qk_backward(const natten_b200_geom* gi, const void* q, const voi
   if (int rc = make_geo(gi, &g)) return rc;
   if (int rc = reject_pitched(g, "qk_backward")) return rc;
   if (any_null({q, k, dlogits, dq, dk})) return set_error(NATTEN_B200_EINVAL, "qk_backward: null tensor");
+  if (any_misaligned({q, k, dlogits, dq, dk})) return reject_misaligned("qk_backward");
   return run_split(SplitOp::QkBackward, g, gi->dtype, q, k, dlogits, nullptr, dq, dk, dbias, (cudaStream_t)stream);
 }
 
@@ -275,6 +288,7 @@ int natten_b200_av_forward(const natten_b200_geom* gi, const void* attn, const v
   if (int rc = make_geo(gi, &g)) return rc;
   if (int rc = reject_pitched(g, "av_forward")) return rc;
   if (any_null({attn, v, out})) return set_error(NATTEN_B200_EINVAL, "av_forward: null tensor");
+  if (any_misaligned({attn, v, out})) return reject_misaligned("av_forward");
   return run_split(SplitOp::AvForward, g, gi->dtype, attn, v, nullptr, nullptr, out, nullptr, nullptr, (cudaStream_t)stream);
 }
 
@@ -284,6 +298,7 @@ int natten_b200_av_backward(const natten_b200_geom* gi, const void* attn, const 
   if (int rc = make_geo(gi, &g)) return rc;
   if (int rc = reject_pitched(g, "av_backward")) return rc;
   if (any_null({attn, v, dout, dattn, dv})) return set_error(NATTEN_B200_EINVAL, "av_backward: null tensor");
+  if (any_misaligned({attn, v, dout, dattn, dv})) return reject_misaligned("av_backward");
   return run_split(SplitOp::AvBackward, g, gi->dtype, attn, v, dout, nullptr, dattn, dv, nullptr, (cudaStream_t)stream);
 }
 
@@ -293,6 +308,7 @@ int natten_b200_fused_forward(const natten_b200_geom* gi, const void* q, const v
   Geo g;
   if (int rc = make_geo(gi, &g)) return rc;
   if (any_null({q, k, v, out})) return set_error(NATTEN_B200_EINVAL, "fused_forward: null tensor");
+  if (any_misaligned({q, k, v, out, k_extra, v_extra})) return reject_misaligned("fused_forward");
   if (g.n_extra > 0 && any_null({k_extra, v_extra}))
     return set_error(NATTEN_B200_EINVAL, "fused_forward: n_extra > 0 needs k_extra and v_extra");
   FusedArgs a{};
@@ -329,6 +345,8 @@ int natten_b200_fused_backward(const natten_b200_geom* gi, const void* q, const 
   if (int rc = make_geo(gi, &g)) return rc;
   if (any_null({q, k, v, out, lse, dout, dq, dk, dv, scratch}))
     return set_error(NATTEN_B200_EINVAL, "fused_backward: null tensor");
+  if (any_misaligned({q, k, v, out, dout, dq, dk, dv, k_extra, v_extra, dk_extra, dv_extra, scratch}))
+    return reject_misaligned("fused_backward");
   if (g.n_extra > 0 && any_null({k_extra, v_extra, dk_extra, dv_extra}))
     return set_error(NATTEN_B200_EINVAL, "fused_backward: n_extra > 0 needs the extra-token tensors");
   if (scratch_bytes < natten_b200_fused_backward_scratch_bytes(gi))
@@ -356,7 +374,10 @@ int natten_b200_fused_backward(const natten_b200_geom* gi, const void* q, const 
 
 int natten_b200_kernel_status(void) { return sm100_read_status(); }
 
-void natten_b200_debug_set_s_dump(float* device_buffer) { sm100_set_debug_s(device_buffer); }
+#ifdef NB_SM100_PROFILE
+// Diagnostic builds only (not part of the ABI): where the tensor-core kernels put their cycle counters.
+void natten_b200_profile_buffer(float* device_buffer) { sm100_set_profile_buffer(device_buffer); }
+#endif
 
 int natten_b200_plan_hint(const natten_b200_geom* gi, int32_t kernel, const int32_t* tile, int32_t max_cols) {
   Geo g;
@@ -387,6 +408,7 @@ int natten_b200_merge_forward(int32_t dtype, int64_t rows, int32_t head_dim, con
   if (rows < 0 || head_dim < 1) return set_error(NATTEN_B200_EINVAL, "merge_forward: bad sizes");
   if (rows == 0) return NATTEN_B200_OK;
   if (any_null({o0, l0, o1, l1, out, lse})) return set_error(NATTEN_B200_EINVAL, "merge_forward: null tensor");
+  if (any_misaligned({o0, o1, out})) return reject_misaligned("merge_forward");
   return run_merge_forward(dtype, rows, head_dim, o0, l0, o1, l1, out, lse, (cudaStream_t)stream);
 }
 
@@ -398,6 +420,7 @@ int natten_b200_merge_backward(int32_t dtype, int64_t rows, int32_t head_dim, co
   if (rows == 0) return NATTEN_B200_OK;
   if (any_null({o0, l0, o1, l1, dout, do0, dl0, do1, dl1}))
     return set_error(NATTEN_B200_EINVAL, "merge_backward: null tensor");
+  if (any_misaligned({o0, o1, dout, do0, do1})) return reject_misaligned("merge_backward");
   return run_merge_backward(dtype, rows, head_dim, o0, l0, o1, l1, dout, dlse, do0, dl0, do1, dl1, (cudaStream_t)stream);
 }
 

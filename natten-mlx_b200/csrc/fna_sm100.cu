@@ -85,7 +85,6 @@ struct FwdParams {
   float* lse;
   int* status;
   unsigned long long* prof;  // optional cycle counters of CTA 0 (diagnostic)
-  float* dbg_s;          // optional [n_chunks of the first work item][128][n_pad] raw S dump
 };
 
 // ---------------------------------------------------------------------------
@@ -208,8 +207,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
   }
   long long best_cost = -1;
   double best_visited = 1.0;
-  int want[3] = {0, 0, 0};                       // tuning aid: pin the tile shape ("t0,t1,t2")
-  if (const char* env_tile = getenv("NATTEN_B200_TILE")) sscanf(env_tile, "%d,%d,%d", &want[0], &want[1], &want[2]);
+  int want[3] = {0, 0, 0};                       // a pinned tile shape (plan_hint)
   if (hint.tile[2] > 0) { want[0] = hint.tile[0]; want[1] = hint.tile[1]; want[2] = hint.tile[2]; }
   for (int t2 = 1; t2 <= p.P; t2 *= 2)
     for (int t1 = 1; t1 * t2 <= p.P; t1 *= 2) {
@@ -312,19 +310,11 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
   // larger chunks.  Every feasible (CTAs, column cap) pair is costed.
   double best = -1.0;
   static const int caps[] = {384, 320, 256, 224, 192, 160, 128, 96, 64, 48, 32};
-  const char* force = getenv("NATTEN_B200_CTAS_PER_SM");   // tuning aid: pin the CTAs per SM
-  const int forced = force != nullptr ? atoi(force) : 0;
-  const char* env_cols = getenv("NATTEN_B200_MAX_COLS");   // tuning aids: cap the chunk width / ring depth
-  const int max_cols = hint.max_cols > 0 ? hint.max_cols : (env_cols != nullptr ? atoi(env_cols) : 0);
-  const char* env_sbuf = getenv("NATTEN_B200_MAX_SBUF");
-  const int max_sbuf = env_sbuf != nullptr ? atoi(env_sbuf) : 0;
-  const char* env_minsb = getenv("NATTEN_B200_MIN_SBUF");
-  const int min_sbuf = env_minsb != nullptr ? atoi(env_minsb) : 0;
+  const int max_cols = hint.max_cols;                       // cap on the chunk width (plan_hint), 0 = none
   // registers per thread of the kernels cap the CTAs per SM: forward 2, dQ 4, dK/dV 2
   const int max_ctas = mode == 1 ? 4 : 2;
   static const double overlap[5] = {0.0, 1.0, 1.7, 2.3, 2.8};
   for (int ctas = max_ctas; ctas >= 1; --ctas) {
-    if (forced >= 1 && forced <= 4 && ctas != (forced < max_ctas ? forced : max_ctas)) continue;
     const int tmem_cols = ctas >= 3 ? 128 : 512 / ctas;   // a power of two per CTA
     const size_t smem_limit = (size_t)(232448 / ctas) - 1024;
     for (int cap : caps) {
@@ -333,8 +323,6 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
       // and single accumulators
       const int acc_cols = mode == 1 ? g.D : 2 * g.D;
       for (int nb = 2; nb >= (mode == 0 ? 2 : 1); --nb) {
-        if (mode != 0 && max_sbuf >= 1 && nb > max_sbuf) continue;
-        if (mode != 0 && min_sbuf >= 1 && nb < min_sbuf) continue;
         const int s_regions = mode == 0 ? nb : 2 * nb;
         if (cap * s_regions > tmem_cols - acc_cols) continue;
         FwdParams p = base;
@@ -346,7 +334,6 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
           // ahead of the others by up to n_sbuf - 1 chunks), one more K/V stage than that
           p.n_sbuf = (tmem_cols - acc_cols) / p.n_pad;
           if (p.n_sbuf > 6) p.n_sbuf = 6;
-          if (max_sbuf >= 2 && p.n_sbuf > max_sbuf) p.n_sbuf = max_sbuf;
           p.kv_stages = p.n_sbuf + 1 > 6 ? 6 : p.n_sbuf + 1;
         }
         while (p.kv_stages > 2 && smem_needed(p) > smem_limit) --p.kv_stages;
@@ -398,14 +385,11 @@ std::map<std::vector<int>, Plan> g_plan_cache;
 std::map<std::vector<int>, PlanHint> g_plan_hints;
 
 Plan make_plan(const Geo& g, int dtype, int mode = 0) {
-  static const bool tuning = getenv("NATTEN_B200_CTAS_PER_SM") || getenv("NATTEN_B200_MAX_COLS") ||
-                             getenv("NATTEN_B200_MAX_SBUF") || getenv("NATTEN_B200_MIN_SBUF") || getenv("NATTEN_B200_TILE");
   std::vector<int> key = plan_key(g, dtype, mode);
   std::lock_guard<std::mutex> lock(g_plan_mu);
   PlanHint hint{{0, 0, 0}, 0};
   auto h = g_plan_hints.find(key);
   if (h != g_plan_hints.end()) hint = h->second;
-  if (tuning) return make_plan_uncached(g, dtype, mode, hint);
   auto it = g_plan_cache.find(key);
   if (it != g_plan_cache.end()) return it->second;
   if (g_plan_cache.size() > 4096) g_plan_cache.clear();   // many distinct per-sample sizes: start over rather than grow

@@ -18,8 +18,8 @@ size_t fused_backward_scratch_sm100(const Geo& g, int dtype);
 // 1 when a tensor-core kernel on the current device gave up on a wait since
 // the last call (synchronises with the device and clears the flag).
 int sm100_read_status();
-// Diagnostic: when set, the forward dumps the raw S of its first tile here.
-void sm100_set_debug_s(float* ptr);
+// Diagnostic builds (-DNB_SM100_PROFILE): buffer that receives the kernels' cycle counters.
+void sm100_set_profile_buffer(float* ptr);
 // Text description of the tiling chosen for a geometry (no GPU needed).
 // mode: 0 forward, 1 dQ kernel, 2 dK/dV kernel.
 int sm100_describe_plan(const Geo& g, int dtype, int mode, char* buf, size_t cap);

@@ -34,6 +34,10 @@ enum class SplitOp { QkForward, QkBackward, AvForward, AvBackward };
 
 int run_split(SplitOp op, const Geo& g, int dtype, const void* a, const void* b, const void* c,
               const float* bias, void* o0, void* o1, float* dbias, cudaStream_t s);
+// Row-per-thread kernels for small head dims (split_rows.cu); false when the shape is not theirs.
+bool run_split_rows(SplitOp op, const Geo& g, int dtype, const void* a, const void* b, const void* c,
+                    const float* bias, void* o0, void* o1, cudaStream_t s);
+bool run_bias_grad_rows(const Geo& g, int dtype, const void* dlogits, float* dbias, cudaStream_t s);
 
 struct FusedArgs {
   const void *q, *k, *v, *k_extra, *v_extra;

@@ -310,9 +310,6 @@ static int launch_split(SplitOp op, const Geo& g, const void* a, const void* b, 
       if (strided) cudaMemsetAsync(o0, 0, (size_t)g.B * g.n_q * g.Hq * g.D * sizeof(T), s);
       wsum(C, Bp, static_cast<T*>(o0), g.scale, 1);
       isum(C, A, static_cast<T*>(o1), g.scale, 0);
-      if (dbias != nullptr) {
-        NB_LAUNCH("bias_grad", s, k_bias_grad<T><<<grid_for(n_logits, 256), 256, 0, s>>>(g, C, dbias));
-      }
       break;
     }
     case SplitOp::AvForward:  // a=attn, b=v -> o0=out
@@ -326,8 +323,23 @@ static int launch_split(SplitOp op, const Geo& g, const void* a, const void* b, 
   return check_launch("split operator");
 }
 
+template <typename T>
+static void launch_bias_grad(const Geo& g, const void* dlogits, float* dbias, cudaStream_t s) {
+  const long long n_logits = (long long)g.B * g.n_out * g.Hq * g.kvol;
+  NB_LAUNCH("bias_grad", s, k_bias_grad<T><<<grid_for(n_logits, 256), 256, 0, s>>>(g, static_cast<const T*>(dlogits), dbias));
+}
+
 int run_split(SplitOp op, const Geo& g, int dtype, const void* a, const void* b, const void* c,
               const float* bias, void* o0, void* o1, float* dbias, cudaStream_t s) {
+  if (op == SplitOp::QkBackward && dbias != nullptr && !run_bias_grad_rows(g, dtype, c, dbias, s)) {
+    // a bias table too large for shared memory: one global atomic per logit
+    switch (dtype) {
+      case NATTEN_B200_F32: launch_bias_grad<float>(g, c, dbias, s); break;
+      case NATTEN_B200_F16: launch_bias_grad<__half>(g, c, dbias, s); break;
+      case NATTEN_B200_BF16: launch_bias_grad<__nv_bfloat16>(g, c, dbias, s); break;
+    }
+  }
+  if (run_split_rows(op, g, dtype, a, b, c, bias, o0, o1, s)) return check_launch("split operator");
   switch (dtype) {
     case NATTEN_B200_F32: return launch_split<float>(op, g, a, b, c, bias, o0, o1, dbias, s);
     case NATTEN_B200_F16: return launch_split<__half>(op, g, a, b, c, bias, o0, o1, dbias, s);

@@ -64,7 +64,10 @@ def _prep(*tensors: torch.Tensor):
             continue
         if t.device != t0.device or t.dtype != t0.dtype:
             raise ValueError("all tensors must share device and dtype")
-        out.append(t.contiguous())
+        t = t.contiguous()
+        if t.data_ptr() % 16 != 0:      # a dense view at an odd storage offset: the kernels need 16-byte aligned bases
+            t = t.clone()
+        out.append(t)
     return out
 
 

@@ -101,6 +101,21 @@ def test_null_pointers_are_rejected():
     assert lib.natten_b200_fused_backward_scratch_bytes(_geom()) >= 16 * 2 * 4
 
 
+def test_misaligned_pointers_are_rejected_before_any_launch():
+    """Rows travel through 16-byte vector accesses and TMA maps: a base address that is not a multiple
+    of 16 is refused with EINVAL on the host (nothing is dereferenced or launched)."""
+    lib = _lib.load()
+    before = _lib.launch_count()
+    assert lib.natten_b200_qk_forward(_geom(), 4096 + 8, 4096, None, 4096, None) == _lib.EINVAL
+    assert "16-byte aligned" in _lib.last_error()
+    assert lib.natten_b200_av_forward(_geom(), 4096, 4096 + 2, 4096, None) == _lib.EINVAL
+    assert lib.natten_b200_fused_forward(_geom(), 4096, 4096, 4096 + 4, None, None, 4096, None, None) == _lib.EINVAL
+    assert lib.natten_b200_fused_backward(_geom(), 4096, 4096, 4096, None, None, 4096, 4096, 4096, None, 4096, 4096 + 12,
+                                          4096, None, None, 4096, 1 << 20, None) == _lib.EINVAL
+    assert lib.natten_b200_merge_forward(0, 4, 8, 4096 + 1, 4096, 4096, 4096, 4096, 4096, None) == _lib.EINVAL
+    assert _lib.launch_count() == before
+
+
 def test_backend_registry():
     assert nb.get_backend() == "cuda"
     with pytest.raises(ValueError):

@@ -47,10 +47,11 @@ def _case(dtype, shape, hkv, ks, dl, ca, n_extra, path):
     _lib.check(lib.natten_b200_fused_forward(geom, _ptr(q), _ptr(k), _ptr(v), _ptr(ke), _ptr(ve), _ptr(out), _ptr(lse),
                                              stream))
 
-    def grads(static):
-        dq, dk, dv = torch.full_like(q, 7.0), torch.full_like(k, 7.0), torch.full_like(v, 7.0)
-        dke = None if ke is None else torch.full_like(ke, 7.0)
-        dve = None if ve is None else torch.full_like(ve, 7.0)
+    def grads(static, outputs=None):
+        if outputs is None:
+            outputs = (torch.full_like(q, 7.0), torch.full_like(k, 7.0), torch.full_like(v, 7.0),
+                       None if ke is None else torch.full_like(ke, 7.0), None if ve is None else torch.full_like(ve, 7.0))
+        dq, dk, dv, dke, dve = outputs
         args = [geom, _ptr(q), _ptr(k), _ptr(v), _ptr(ke), _ptr(ve), _ptr(out), _ptr(lse), _ptr(dout), _ptr(dlse),
                 _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dke), _ptr(dve)]
         if static:
@@ -79,6 +80,17 @@ def test_static_scratch_backward_matches_regular_entry_point(dtype, shape, hkv, 
             err = (a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6)
             assert err <= tol, (attempt, float(err))
     assert _lib.kernel_status() == 0
+    # The entry point's one promise: with the outputs already in place, a call leaves the device's free memory
+    # and torch's reserved pool exactly as it found them (the first call on the device, above, did the set-up).
+    outputs = tuple(torch.full_like(t, 7.0) for t in want) + (None,) * (5 - len(want))
+    torch.cuda.synchronize()
+    free_before, reserved_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+    got = grads(static=True, outputs=outputs)
+    free_after, reserved_after = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+    assert reserved_after == reserved_before
+    assert free_after >= free_before, (free_before, free_after)
+    for a, b in zip(got, want):
+        assert (a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-6) <= tol
 
 
 def test_static_scratch_refuses_oversized_geometry():
