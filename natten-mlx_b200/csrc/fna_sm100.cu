@@ -336,6 +336,7 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
           if (p.n_sbuf > 6) p.n_sbuf = 6;
           p.kv_stages = p.n_sbuf + 1 > 6 ? 6 : p.n_sbuf + 1;
         }
+
         while (p.kv_stages > 2 && smem_needed(p) > smem_limit) --p.kv_stages;
         if (smem_needed(p) > smem_limit) p.q_stages = 1;
         if (smem_needed(p) > smem_limit) continue;           // a single chunk stage would lose the prefetch
