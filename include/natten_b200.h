@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define NATTEN_B200_ABI_VERSION 1
+#define NATTEN_B200_ABI_VERSION 2
 
 enum {
   NATTEN_B200_OK = 0,
@@ -64,7 +64,15 @@ enum {
  * extents, when not NULL, is a device array [batch, rank] int32 with the
  * valid extent of each sample inside the padded tensors (variable-size
  * batches); it replaces global_extent per sample, and queries outside it
- * produce zeros.
+ * produce zeros (CUDA-core kernels) or are left unwritten (tensor-core kernels:
+ * hand them zero-filled outputs).  host_extents, when not NULL, is a host copy
+ * of the same array: with it the fused entry points can serve a variable-size
+ * batch on the tensor-core kernels in one launch per kernel (every sample gets
+ * TMA tensor maps with its own bounds, built on the host, so that padding of
+ * any content, NaN included, stays out of the arithmetic, as with the
+ * reference's per-sample slices, src/natten_mlx/_core/pure.py:559-577);
+ * without it such a batch runs on the CUDA-core kernels.  The host array is
+ * read during the call only.
  *
  * mem_extent, when not all zero, says that every tensor of the call (q, k, v,
  * out, lse and the gradients) is the leading corner of a larger dense array
@@ -100,6 +108,7 @@ typedef struct natten_b200_geom {
   const int32_t* extents;   /* device, [batch, rank], or NULL                     */
   int32_t mem_extent[3];    /* all zero: dense tensors; see above                 */
   int32_t reserved;         /* must be zero                                       */
+  const int32_t* host_extents; /* host copy of extents, or NULL                    */
 } natten_b200_geom;
 
 int natten_b200_abi_version(void);

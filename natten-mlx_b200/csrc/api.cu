@@ -17,7 +17,8 @@
 #include <stddef.h>
 
 // The ctypes mirror of the geometry struct relies on this layout.
-static_assert(sizeof(natten_b200_geom) == 168, "natten_b200_geom layout changed");
+static_assert(sizeof(natten_b200_geom) == 176, "natten_b200_geom layout changed");
+static_assert(offsetof(natten_b200_geom, host_extents) == 168, "natten_b200_geom layout changed");
 static_assert(offsetof(natten_b200_geom, mem_extent) == 152, "natten_b200_geom layout changed");
 static_assert(offsetof(natten_b200_geom, scale) == 132, "natten_b200_geom layout changed");
 static_assert(offsetof(natten_b200_geom, extents) == 144, "natten_b200_geom layout changed");
@@ -93,6 +94,7 @@ int make_geo(const natten_b200_geom* in, Geo* g) {
   g->B = in->batch; g->Hq = in->heads_q; g->Hkv = in->heads_kv; g->rep = in->heads_q / in->heads_kv;
   g->D = in->head_dim; g->rank = in->rank; g->scale = in->scale; g->n_extra = in->n_extra;
   g->extents = in->extents;
+  g->host_extents = in->extents != nullptr ? in->host_extents : nullptr;
   const int lead = 3 - in->rank;
   for (int a = 0; a < 3; ++a) {
     g->qe[a] = g->ke[a] = g->ge[a] = 1;

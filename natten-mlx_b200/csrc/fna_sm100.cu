@@ -44,6 +44,7 @@ struct alignas(64) TmaMaps {
   CUtensorMap q[kMaxClasses];
   CUtensorMap k[kMaxClasses];
   CUtensorMap v[kMaxClasses];
+  CUtensorMap xk, xv;   // extra tokens [B, N_extra, Hkv, D]
 };
 
 // Backward: r1/r2 are the row operands of a tile (Q, dO | K, V), c1/c2 the
@@ -53,6 +54,7 @@ struct alignas(64) TmaMapsBwd {
   CUtensorMap r2[kMaxClasses];
   CUtensorMap c1[kMaxClasses];
   CUtensorMap c2[kMaxClasses];
+  CUtensorMap xk, xv;   // extra tokens: chunk operands of the dQ kernel, row operands of the dK/dV kernel's extra-token items
 };
 
 struct FwdParams {
@@ -81,6 +83,19 @@ struct FwdParams {
   float scale_log2;
   uint32_t idesc_qk, idesc_pv;
   int is_bf16;
+  // variable-size batches: per-sample extents on the device, and the tensor maps of every (sample, dilation class)
+  // in global memory, `nmaps` per pair in the order of the parameter maps (q k v | r1 r2 c1 c2)
+  const int* extents;
+  const CUtensorMap* gmaps;
+  int nmaps;
+  // extra tokens: count, tokens per extra chunk (a chunk of xw tokens follows the chunks of the key box in the
+  // forward and dQ kernels), number of such chunks
+  int n_extra, xw, n_xchunks;
+  // dK/dV kernel: the work items after n_work_main own the extra tokens (rows = a tile of 128 tokens, chunks = one
+  // box of a dilation class's queries, xr[a] boxes per axis); their partial sums go to float32 accumulators
+  long long n_work_main;
+  int n_xtiles, xr[3];
+  float *acc_k, *acc_v;
   void* out;
   float* lse;
   int* status;
@@ -188,6 +203,31 @@ double mean_needed_fraction(int L, int K, int d, int T, int box, bool rows_are_q
   return n > 0 ? sum / n : 1.0;
 }
 
+// max_query_span over the extents the axis takes in this call: the global extent, or every distinct sample
+// extent of a variable-size batch (results are kept: the planner asks for the same few values again and again).
+int query_span(const Geo& g, int a, int T) {
+  static std::mutex mu;
+  static std::map<std::vector<int>, int> memo;
+  auto one = [&](int L) {
+    const std::vector<int> key = {L, g.K[a], g.dl[a], T};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+    if (memo.size() > 65536) memo.clear();
+    const int v = max_query_span(L, g.K[a], g.dl[a], T);
+    memo.emplace(key, v);
+    return v;
+  };
+  const int lead = 3 - g.rank;
+  if (g.host_extents == nullptr || a < lead) return one(g.ge[a]);
+  int best = 0;
+  for (int b = 0; b < g.B; ++b) {
+    const int v = one(g.host_extents[b * g.rank + (a - lead)]);
+    if (v > best) best = v;
+  }
+  return best;
+}
+
 // Best query tile for a cap of `nmax` S columns per chunk; returns the cost
 // (tiles x chunks x padded columns) or -1 when nothing fits.
 // A pinned tile shape and chunk-width cap for one geometry and kernel (plan_hint entry point); zeros pin nothing.
@@ -220,7 +260,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
         // keys a query tile addresses: T + K - 1; queries that address a key tile: more near the
         // ends of the axis (see max_query_span)
         int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1;
-        if (mode == 2 && g.ca[a] == 0) need = max_query_span(g.ge[a], g.K[a], g.dl[a], T[a]);
+        if (mode == 2 && g.ca[a] == 0) need = query_span(g, a, T[a]);
         box[a] = need < lgmax[a] ? need : lgmax[a];
         if (box[a] > 256) skip = true;                        // TMA box limit
       }
@@ -250,7 +290,9 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
       for (int a = 0; a < 2; ++a)
         if (g.ge[a] > 1 && g.ca[a] == 0 && box[a] > 1)
           visited *= mean_needed_fraction(g.ge[a], g.K[a], g.dl[a], T[a], box[a], mode != 2);
-      const long long cost = tiles * nch * (n_pad + 96);      // +96: fixed per-chunk overhead
+      // +96: fixed per-chunk overhead; boxes without row structure go through per-row bitmaps, which cost the
+      // elementwise warps about half as much again
+      const long long cost = tiles * nch * (n_pad + 96) * (rp == 0 ? 3 : 2) / 2;
       if (best_cost < 0 || cost < best_cost || (cost == best_cost && visited < best_visited - 1e-9)) {
         best_cost = cost;
         best_visited = visited;
@@ -268,8 +310,19 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
   FwdParams base{};
   if (dtype != NATTEN_B200_BF16 && dtype != NATTEN_B200_F16) { pl.why = "dtype is not bf16/f16"; return pl; }
   if (g.D != 32 && g.D != 64 && g.D != 128) { pl.why = "head_dim is not 32, 64 or 128"; return pl; }
-  if (g.n_extra != 0) { pl.why = "extra tokens"; return pl; }
-  if (g.extents != nullptr) { pl.why = "per-sample extents"; return pl; }
+  if (g.extents != nullptr && g.host_extents == nullptr) { pl.why = "per-sample extents without a host copy"; return pl; }
+  const bool varlen = g.extents != nullptr;
+  if (varlen) {
+    const int lead = 3 - g.rank;
+    for (int b = 0; b < g.B; ++b)
+      for (int a = 0; a < g.rank; ++a) {
+        const int e = g.host_extents[b * g.rank + a];
+        if (e > g.ge[lead + a] || (long long)g.K[lead + a] * g.dl[lead + a] > e) {
+          pl.why = "a sample extent is larger than the tensors or smaller than kernel_size * dilation";
+          return pl;
+        }
+      }
+  }
   if (!(g.scale > 0.f)) { pl.why = "scale is not positive"; return pl; }
   int ncls = 1;
   for (int a = 0; a < 3; ++a) {
@@ -278,6 +331,7 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
       pl.why = "slab on an axis other than the leading axis of a 3-D volume";
       return pl;
     }
+    if ((g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a]) && g.n_extra != 0) { pl.why = "extra tokens with a slab"; return pl; }
     ncls *= g.dl[a];
   }
   if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
@@ -356,7 +410,29 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
   p.n_split = p.n_pad > 256 ? 2 : 1;
   p.n_half = p.n_pad / p.n_split;
   pl.smem = smem_needed(p);
-  const long long n_work = (long long)g.B * g.Hkv * p.head_groups * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
+  long long n_work = (long long)g.B * g.Hkv * p.head_groups * ncls * p.tiles[0] * p.tiles[1] * p.tiles[2];
+  p.n_work_main = n_work;
+  p.n_extra = g.n_extra;
+  p.xw = p.n_xchunks = p.n_xtiles = 0;
+  p.xr[0] = p.xr[1] = p.xr[2] = 1;
+  if (g.n_extra > 0) {
+    // forward / dQ: the extra tokens follow the key box as chunks of xw tokens (one TMA box: at most 256 rows)
+    p.xw = p.n_pad < 256 ? p.n_pad : 256;
+    p.n_xchunks = ceil_div(g.n_extra, p.xw);
+    if (mode != 2) {
+      p.xw = (ceil_div(g.n_extra, p.n_xchunks) + 15) & ~15;     // even out the chunks
+    } else {
+      // dK/dV: tiles of 128 extra tokens, each walking every box of every dilation class's queries
+      p.n_xchunks = 0;
+      p.n_xtiles = ceil_div(g.n_extra, kTileM);
+      long long regions = 1;
+      for (int a = 0; a < 3; ++a) {
+        p.xr[a] = ceil_div(ceil_div(g.ge[a], g.dl[a]), p.box[a]);
+        regions *= p.xr[a];
+      }
+      n_work += (long long)g.B * g.Hkv * p.n_xtiles * ncls * regions;
+    }
+  }
   if (n_work >= (1LL << 31)) { pl.why = "more than 2^31 tiles"; return pl; }
   p.n_work = n_work;
   p.scale_log2 = g.scale * 1.4426950408889634f;
@@ -378,6 +454,9 @@ std::vector<int> plan_key(const Geo& g, int dtype, int mode) {
   key.push_back(scale_bits);
   for (int a = 0; a < 3; ++a)
     for (int v : {g.qe[a], g.ke[a], g.ge[a], g.me[a], g.qo[a], g.ko[a], g.K[a], g.st[a], g.dl[a], g.ca[a]}) key.push_back(v);
+  key.push_back(g.host_extents != nullptr ? 1 : 0);
+  if (g.extents != nullptr && g.host_extents != nullptr)   // the dK/dV query box depends on the sample extents
+    for (int i = 0; i < g.B * g.rank; ++i) key.push_back(g.host_extents[i]);
   return key;
 }
 
@@ -493,6 +572,44 @@ int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, i
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return set_error(NATTEN_B200_ELAUNCH, "cuTensorMapEncodeTiled failed with code %d", (int)r);
       }
+  return 0;
+}
+
+// Map of the extra tokens [B, N_extra, Hkv, D]: dims (Hkv * D, N_extra, B), box (dblk, rows, 1).  Rows past N_extra
+// read as zeros.
+int encode_extra_map(CUtensorMap* map, const void* base, const FwdParams& p, int heads, int n_extra, int rows) {
+  EncodeTiledFn enc = encode_fn();
+  if (enc == nullptr) return set_error(NATTEN_B200_ENODEVICE, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[3] = {(cuuint64_t)heads * p.D, (cuuint64_t)n_extra, (cuuint64_t)p.B};
+  cuuint64_t strides[2] = {(cuuint64_t)heads * p.D * 2, (cuuint64_t)n_extra * heads * p.D * 2};
+  cuuint32_t box[3] = {(cuuint32_t)p.dblk, (cuuint32_t)rows, 1}, estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, p.is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         p.D == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(NATTEN_B200_ELAUNCH, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+// Variable-size batch: the class maps of one tensor for every sample, each with the sample's own bounds (strides
+// stay those of the padded tensor), written to out[(b * ncls + cls) * nmaps + which].
+int encode_sample_maps(std::vector<CUtensorMap>& out, int nmaps, int which, const void* base, const FwdParams& p, int heads,
+                       const int box_sp[3], bool chunk_side, const int* host_extents) {
+  int ncls = p.dl[0] * p.dl[1] * p.dl[2];
+  const int lead = 3 - p.rank;
+  const int* ext = chunk_side ? p.Mc : p.Mr;
+  const long long batch_el = (long long)heads * p.D * ext[0] * ext[1] * ext[2];
+  CUtensorMap tmp[kMaxClasses];
+  for (int b = 0; b < p.B; ++b) {
+    FwdParams pb = p;
+    pb.B = 1;
+    for (int a = 0; a < p.rank; ++a) pb.L[lead + a] = host_extents[b * p.rank + a];
+    pb.ro0 = pb.co0 = 0;
+    pb.re0 = pb.ce0 = pb.L[0];
+    const char* sample = static_cast<const char*>(base) + (long long)b * batch_el * 2;
+    if (int rc = encode_class_maps(tmp, sample, pb, heads, box_sp, chunk_side)) return rc;
+    for (int c = 0; c < ncls; ++c) out[((size_t)b * ncls + c) * nmaps + which] = tmp[c];
+  }
   return 0;
 }
 

@@ -82,6 +82,7 @@ struct Geo {
   int kvol, n_extra;
   float scale;
   const int* extents;  // [B, rank] or nullptr
+  const int* host_extents;  // host copy of extents (lets the tensor-core kernels take a variable-size batch) or nullptr
   long long n_out;     // out[0]*out[1]*out[2]
   long long n_q;       // qe[0]*qe[1]*qe[2]
   long long n_kv;      // ke[0]*ke[1]*ke[2]

@@ -95,7 +95,7 @@ def _sizes_tensor(sizes, batch, rank, device):
 
 
 def _geom(q_like, kv_like, rank, ks, st, dl, ca, scale, *, heads_q=None, n_extra=0, sizes=None,
-          slab: Optional[Slab] = None, path=None):
+          slab: Optional[Slab] = None, path=None, host_sizes=None):
     extent = tuple(q_like.shape[1:1 + rank])
     kv_extent = tuple(kv_like.shape[1:1 + rank])
     kw = {}
@@ -108,7 +108,8 @@ def _geom(q_like, kv_like, rank, ks, st, dl, ca, scale, *, heads_q=None, n_extra
         rank, q_like.shape[0], heads_q if heads_q is not None else q_like.shape[-2], kv_like.shape[-2],
         kv_like.shape[-1], _DTYPES[kv_like.dtype], extent, ks, st, dl, ca, scale, n_extra=n_extra,
         path=_PATHS[_fused_path] if path is None else _PATHS[path],
-        extents_ptr=0 if sizes is None else sizes.data_ptr(), **kw)
+        extents_ptr=0 if sizes is None else sizes.data_ptr(),
+        host_extents=None if sizes is None else host_sizes, **kw)
 
 
 # ---------------------------------------------------------------------------
@@ -187,18 +188,30 @@ def av_backward(attn, v, grad_out, ks, st, dl, ca):
 # fused operator
 # ---------------------------------------------------------------------------
 
+def _host_sizes(sizes, host_sizes, batch, rank):
+    """Per-sample extents as a host list of ``rank``-tuples: the caller's copy, or one read back from the device
+    tensor (a synchronising copy; pass ``host_sizes`` to avoid it)."""
+    if sizes is None:
+        return None
+    if host_sizes is None:
+        host_sizes = (sizes.detach().cpu() if torch.is_tensor(sizes) else torch.as_tensor(sizes)).reshape(batch, rank).tolist()
+    return [tuple(int(x) for x in (s if isinstance(s, (list, tuple)) else (s,))) for s in host_sizes]
+
+
 def fused_forward(q, k, v, ks, st, dl, ca, scale, *, k_extra=None, v_extra=None, sizes=None,
-                  slab: Optional[Slab] = None, path=None):
-    """Returns (out, lse); lse is float32 [B, out..., H_q]."""
+                  slab: Optional[Slab] = None, path=None, host_sizes=None):
+    """Returns (out, lse); lse is float32 [B, out..., H_q].  With per-sample ``sizes`` the padding of both is zero."""
     rank = q.dim() - 3
     q, k, v, k_extra, v_extra = _prep(q, k, v, k_extra, v_extra)
     n_extra = 0 if k_extra is None else k_extra.shape[1]
     sizes_t = _sizes_tensor(sizes, q.shape[0], rank, q.device)
     g = _geom(q, k, rank, ks, st, dl, ca, _scale(scale, q.shape[-1]), n_extra=n_extra, sizes=sizes_t,
-              slab=slab, path=path)
+              slab=slab, path=path, host_sizes=_host_sizes(sizes, host_sizes, q.shape[0], rank))
     outs = _out_shape(q.shape[1:1 + rank], st)
-    out = torch.empty((q.shape[0],) + outs + tuple(q.shape[-2:]), dtype=q.dtype, device=q.device)
-    lse = torch.empty((q.shape[0],) + outs + (q.shape[-2],), dtype=torch.float32, device=q.device)
+    # variable-size batches: the tensor-core kernels never touch rows outside a sample, so they start from zeros
+    alloc = torch.empty if sizes is None else torch.zeros
+    out = alloc((q.shape[0],) + outs + tuple(q.shape[-2:]), dtype=q.dtype, device=q.device)
+    lse = alloc((q.shape[0],) + outs + (q.shape[-2],), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
         _lib.check(_lib.load().natten_b200_fused_forward(g, _ptr(q), _ptr(k), _ptr(v), _ptr(k_extra), _ptr(v_extra),
                                                          _ptr(out), _ptr(lse), _stream(q)))
@@ -206,18 +219,19 @@ def fused_forward(q, k, v, ks, st, dl, ca, scale, *, k_extra=None, v_extra=None,
 
 
 def fused_backward(q, k, v, out, lse, grad_out, grad_lse, ks, st, dl, ca, scale, *, k_extra=None,
-                   v_extra=None, sizes=None, slab: Optional[Slab] = None, path=None):
+                   v_extra=None, sizes=None, slab: Optional[Slab] = None, path=None, host_sizes=None):
     """Returns (dq, dk, dv, dk_extra, dv_extra); the last two are None without extra tokens."""
     rank = q.dim() - 3
     q, k, v, k_extra, v_extra, out, grad_out = _prep(q, k, v, k_extra, v_extra, out, grad_out)
     n_extra = 0 if k_extra is None else k_extra.shape[1]
     sizes_t = _sizes_tensor(sizes, q.shape[0], rank, q.device)
     g = _geom(q, k, rank, ks, st, dl, ca, _scale(scale, q.shape[-1]), n_extra=n_extra, sizes=sizes_t,
-              slab=slab, path=path)
+              slab=slab, path=path, host_sizes=_host_sizes(sizes, host_sizes, q.shape[0], rank))
     lse = lse.contiguous()
     if grad_lse is not None:
         grad_lse = grad_lse.to(torch.float32).contiguous()
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    alloc = torch.empty_like if sizes is None else torch.zeros_like     # see fused_forward
+    dq, dk, dv = alloc(q), alloc(k), alloc(v)
     dke = None if k_extra is None else torch.empty_like(k_extra)
     dve = None if v_extra is None else torch.empty_like(v_extra)
     lib = _lib.load()
@@ -228,74 +242,6 @@ def fused_backward(q, k, v, out, lse, grad_out, grad_lse, ks, st, dl, ca, scale,
             g, _ptr(q), _ptr(k), _ptr(v), _ptr(k_extra), _ptr(v_extra), _ptr(out), _ptr(lse), _ptr(grad_out),
             _ptr(grad_lse), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dke), _ptr(dve), _ptr(scratch), nbytes, _stream(q)))
     return dq, dk, dv, dke, dve
-
-
-# ---------------------------------------------------------------------------
-# variable-size batches on the tensor-core kernels: one call per sample
-# ---------------------------------------------------------------------------
-# The kernels take a sample as the leading corner of its padded block
-# (``mem_extent`` of the C geometry): strides come from the padded extents,
-# bounds and windows from the sample's own, so padding of any content stays
-# out of the arithmetic and is never written.  The reference slices each
-# sample out and pads the result (src/natten_mlx/_core/pure.py:559-577).
-
-def _sample_geom(q, k, rank, size, ks, dl, scale):
-    one, no = (1,) * rank, (False,) * rank
-    return _lib.make_geom(rank, 1, q.shape[-2], k.shape[-2], q.shape[-1], _DTYPES[q.dtype], size, ks, one, dl, no,
-                          scale, path=_lib.PATH_TCGEN05, mem_extent=tuple(q.shape[1:1 + rank]))
-
-
-def per_sample_tensor_core_ok(q, k, host_sizes, ks, dl, scale) -> bool:
-    """True when every sample size has tensor-core plans for the forward and both backward kernels."""
-    if _fused_path == "simt" or not q.is_cuda or q.dtype not in (torch.float16, torch.bfloat16):
-        return False
-    rank = q.dim() - 3
-    for size in sorted(set(tuple(int(x) for x in s) for s in host_sizes)):
-        try:
-            plan = _lib.describe_plan(_sample_geom(q, k, rank, size, ks, dl, _scale(scale, q.shape[-1])))
-        except ValueError:
-            return False
-        if "unsupported" in plan:
-            return False
-    return True
-
-
-def fused_forward_per_sample(q, k, v, host_sizes, ks, dl, scale):
-    """(out, lse) with zeros in the padding; q/k/v ``[B, padded spatial..., heads, D]``."""
-    rank = q.dim() - 3
-    q, k, v = _prep(q, k, v)
-    out = torch.zeros_like(q)
-    lse = torch.zeros(q.shape[:-1], dtype=torch.float32, device=q.device)
-    lib, sc = _lib.load(), _scale(scale, q.shape[-1])
-    with torch.cuda.device(q.device):
-        stream = _stream(q)
-        for b, size in enumerate(host_sizes):
-            g = _sample_geom(q, k, rank, tuple(int(x) for x in size), ks, dl, sc)
-            _lib.check(lib.natten_b200_fused_forward(g, _ptr(q[b]), _ptr(k[b]), _ptr(v[b]), None, None, _ptr(out[b]),
-                                                     _ptr(lse[b]), stream))
-    return out, lse
-
-
-def fused_backward_per_sample(q, k, v, out, lse, grad_out, grad_lse, host_sizes, ks, dl, scale):
-    """(dq, dk, dv) with zeros in the padding."""
-    rank = q.dim() - 3
-    q, k, v, out, grad_out = _prep(q, k, v, out, grad_out)
-    lse = lse.contiguous()
-    if grad_lse is not None:
-        grad_lse = grad_lse.to(torch.float32).contiguous()
-    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
-    lib, sc = _lib.load(), _scale(scale, q.shape[-1])
-    geoms = [_sample_geom(q, k, rank, tuple(int(x) for x in size), ks, dl, sc) for size in host_sizes]
-    nbytes = max(int(lib.natten_b200_fused_backward_scratch_bytes(g)) for g in geoms)
-    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)   # the calls run in stream order
-    with torch.cuda.device(q.device):
-        stream = _stream(q)
-        for b, g in enumerate(geoms):
-            _lib.check(lib.natten_b200_fused_backward(
-                g, _ptr(q[b]), _ptr(k[b]), _ptr(v[b]), None, None, _ptr(out[b]), _ptr(lse[b]), _ptr(grad_out[b]),
-                None if grad_lse is None else _ptr(grad_lse[b]), _ptr(dq[b]), _ptr(dk[b]), _ptr(dv[b]), None, None,
-                _ptr(scratch), nbytes, stream))
-    return dq, dk, dv
 
 
 # ---------------------------------------------------------------------------

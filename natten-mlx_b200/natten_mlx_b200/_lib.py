@@ -47,6 +47,7 @@ class Geom(ctypes.Structure):
         ("extents", ctypes.c_void_p),
         ("mem_extent", _I3),
         ("reserved", ctypes.c_int32),
+        ("host_extents", ctypes.c_void_p),
     ]
 
 
@@ -99,7 +100,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = res
         fn.argtypes = args
-    if lib.natten_b200_abi_version() != 1:
+    if lib.natten_b200_abi_version() != 2:
         raise ImportError("libnatten_b200.so has an unexpected ABI version")
     _lib = lib
     return lib
@@ -160,7 +161,7 @@ def make_geom(rank: int, batch: int, heads_q: int, heads_kv: int, head_dim: int,
               n_extra: int = 0, path: int = PATH_AUTO, extents_ptr: int = 0,
               q_extent: Optional[Sequence[int]] = None, kv_extent: Optional[Sequence[int]] = None,
               q_offset: Optional[Sequence[int]] = None, kv_offset: Optional[Sequence[int]] = None,
-              mem_extent: Optional[Sequence[int]] = None) -> Geom:
+              mem_extent: Optional[Sequence[int]] = None, host_extents: Optional[Sequence[Sequence[int]]] = None) -> Geom:
     def arr(v, fill=0):
         v = list(v) + [fill] * (3 - len(v))
         return _I3(*[int(x) for x in v])
@@ -180,4 +181,10 @@ def make_geom(rank: int, batch: int, heads_q: int, heads_kv: int, head_dim: int,
     g.extents = extents_ptr or None
     g.mem_extent = arr(mem_extent if mem_extent is not None else [0] * rank)
     g.reserved = 0
+    g.host_extents = None
+    if host_extents is not None:
+        flat = [int(x) for row in host_extents for x in (row if isinstance(row, (list, tuple)) else (row,))]
+        arr_t = (ctypes.c_int32 * len(flat))(*flat)
+        g._host_extents_keepalive = arr_t            # the struct only holds the address
+        g.host_extents = ctypes.cast(arr_t, ctypes.c_void_p).value
     return g

@@ -19,12 +19,13 @@ class _FusedNA(torch.autograd.Function):
     """(out, lse) = attention over the window (and extra tokens)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, k_extra, v_extra, sizes, ks, st, dl, ca, scale):
+    def forward(ctx, q, k, v, k_extra, v_extra, sizes, ks, st, dl, ca, scale, host_sizes=None):
         backend = ops._backend_module()
         out, lse = backend.fused_forward(q, k, v, ks, st, dl, ca, scale, k_extra=k_extra, v_extra=v_extra,
-                                         sizes=sizes)
+                                         sizes=sizes, host_sizes=host_sizes)
         ctx.save_for_backward(q, k, v, k_extra, v_extra, out, lse)
         ctx.sizes = sizes
+        ctx.host_sizes = host_sizes
         ctx.params = (ks, st, dl, ca, scale)
         ctx.mark_non_differentiable()
         return out, lse
@@ -38,79 +39,8 @@ class _FusedNA(torch.autograd.Function):
             grad_out = torch.zeros_like(out)
         dq, dk, dv, dke, dve = backend.fused_backward(
             q, k, v, out, lse, grad_out, grad_lse, ks, st, dl, ca, scale, k_extra=k_extra, v_extra=v_extra,
-            sizes=ctx.sizes)
-        return dq, dk, dv, dke, dve, None, None, None, None, None, None
-
-
-class _PerSampleNA(torch.autograd.Function):
-    """(out, lse) of a variable-size batch, one tensor-core call per sample; zeros in the padding."""
-
-    @staticmethod
-    def forward(ctx, q, k, v, host_sizes, ks, dl, scale):
-        backend = ops._backend_module()
-        out, lse = backend.fused_forward_per_sample(q, k, v, host_sizes, ks, dl, scale)
-        ctx.save_for_backward(q, k, v, out, lse)
-        ctx.params = (host_sizes, ks, dl, scale)
-        return out, lse
-
-    @staticmethod
-    def backward(ctx, grad_out, grad_lse):
-        q, k, v, out, lse = ctx.saved_tensors
-        host_sizes, ks, dl, scale = ctx.params
-        backend = ops._backend_module()
-        if grad_out is None:
-            grad_out = torch.zeros_like(out)
-        dq, dk, dv = backend.fused_backward_per_sample(q, k, v, out, lse, grad_out, grad_lse, host_sizes, ks, dl,
-                                                       scale)
-        return dq, dk, dv, None, None, None, None
-
-
-class _DenseExtra(torch.autograd.Function):
-    """Dense attention of every query over a few extra tokens, returning (out, lse) with gradients
-    through both: torch's flash scaled-dot-product kernel (a library kernel for a plain dense
-    attention, as the reference's ``mx.fast.scaled_dot_product_attention``, functional.py:176).
-    The library's backward knows nothing of a gradient on the log-sum-exp; that term is
-    ``dq += dlse * scale * softmax(S) K`` (one more forward with V := K) and
-    ``dK += scale * softmax(S)^T (dlse * q)`` (the value gradient of one more backward)."""
-
-    @staticmethod
-    def forward(ctx, q, ak, av, scale):
-        rep = q.shape[-2] // ak.shape[-2]
-        qt = q.transpose(1, 2)                                            # [B, Hq, N, D]
-        kk = ak.repeat_interleave(rep, dim=2).transpose(1, 2).contiguous()  # [B, Hq, X, D]
-        vv = av.repeat_interleave(rep, dim=2).transpose(1, 2).contiguous()
-        res = torch.ops.aten._scaled_dot_product_flash_attention(qt, kk, vv, 0.0, False, False, scale=scale)
-        ctx.save_for_backward(qt, kk, vv, res[0], res[1], res[2], res[3], res[6], res[7])
-        ctx.meta = (res[4], res[5], float(scale), rep)
-        return res[0].transpose(1, 2), res[1].transpose(1, 2)
-
-    @staticmethod
-    def backward(ctx, grad_out, grad_lse):
-        qt, kk, vv, out, lse, cq, ck, seed, offset = ctx.saved_tensors
-        max_q, max_k, scale, rep = ctx.meta
-        op_f = torch.ops.aten._scaled_dot_product_flash_attention
-        op_b = torch.ops.aten._scaled_dot_product_flash_attention_backward
-        go = torch.zeros_like(out) if grad_out is None else grad_out.transpose(1, 2)   # strided view: no copy
-        dq, dk, dv = op_b(go, qt, kk, vv, out, lse, cq, ck, max_q, max_k, 0.0, False, seed, offset, scale=scale)
-        if grad_lse is not None:
-            gl = (grad_lse.transpose(1, 2) * scale).to(qt.dtype)[..., None]           # [B, Hq, N, 1]
-            res = op_f(qt, kk, kk, 0.0, False, False, scale=scale)
-            dq.addcmul_(gl, res[0])
-            _, _, dk_l = op_b(gl * qt, qt, kk, kk, res[0], res[1], res[2], res[3], res[4], res[5],
-                              0.0, False, res[6], res[7], scale=scale)
-            dk = dk + dk_l
-        b, hq, x, d = dk.shape
-        fold = lambda t: t.view(b, hq // rep, rep, x, d).float().sum(2).to(t.dtype).transpose(1, 2)   # [B, X, Hkv, D]
-        return dq.transpose(1, 2), fold(dk), fold(dv), None
-
-
-def dense_extra_with_grad(q, ak, av, scale):
-    """(out [B, N, Hq, D], lse [B, N, Hq]) of dense attention over the extra tokens."""
-    return _DenseExtra.apply(q, ak, av, scale)
-
-
-def per_sample_with_grad(q, k, v, host_sizes, ks, dl, scale):
-    return _PerSampleNA.apply(q, k, v, host_sizes, ks, dl, scale)
+            sizes=ctx.sizes, host_sizes=ctx.host_sizes)
+        return dq, dk, dv, dke, dve, None, None, None, None, None, None, None
 
 
 class _QK(torch.autograd.Function):
@@ -178,9 +108,10 @@ class _Merge(torch.autograd.Function):
         return do0, dl0.to(l0.dtype), do1, dl1.to(l1.dtype)
 
 
-def fused_with_grad(q, k, v, ks, st, dl, ca, scale, k_extra=None, v_extra=None, sizes=None):
-    """(out, lse) with gradients for q, k, v and the extra tokens."""
-    return _FusedNA.apply(q, k, v, k_extra, v_extra, sizes, ks, st, dl, ca, scale)
+def fused_with_grad(q, k, v, ks, st, dl, ca, scale, k_extra=None, v_extra=None, sizes=None, host_sizes=None):
+    """(out, lse) with gradients for q, k, v and the extra tokens.  ``host_sizes`` is a host copy of the per-sample
+    ``sizes`` (it lets a variable-size batch run on the tensor-core kernels without a device-to-host copy)."""
+    return _FusedNA.apply(q, k, v, k_extra, v_extra, sizes, ks, st, dl, ca, scale, host_sizes)
 
 
 def _named(rank):

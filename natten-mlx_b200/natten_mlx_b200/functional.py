@@ -6,12 +6,17 @@ Differences in how the work is done, not in what is computed:
 * GQA/MQA never materialises repeated K/V heads; the kernels index the KV head
   as ``h // (H_q / H_kv)`` (the reference repeats, functional.py:29-33).
 * ``return_lse`` and ``additional_keys/values`` run inside the one fused
-  kernel (window slots and extra tokens share a softmax) instead of the
-  split-QK -> softmax -> AV -> dense attention -> merge chain of
-  functional.py:276-292; the results are the same function of the inputs.
+  kernel of either family (window slots and extra tokens share a softmax: on
+  the tensor-core kernels the extra tokens are one more chunk of keys after
+  the key box) instead of the split-QK -> softmax -> AV -> dense attention ->
+  merge chain of functional.py:276-292; the results are the same function of
+  the inputs.
 * A kernel that covers the whole extent takes the same fused kernel (the
   reference routes it to a dense-attention library call, functional.py:141-187).
-* The varlen ops also accept GQA, ``return_lse`` and extra tokens.
+* The varlen ops also accept GQA, ``return_lse`` and extra tokens, and take
+  ``host_sizes`` (a host copy of the sizes): with it a bf16/fp16 batch runs
+  on the tensor-core kernels in one launch per kernel without a
+  device-to-host copy.
 """
 
 from __future__ import annotations
@@ -100,15 +105,6 @@ def _na(rank, query, key, value, kernel_size, stride, dilation, is_causal, scale
     if all(k >= e for k, e in zip(ks, spatial)) and all(s == 1 for s in st) and not any(ca):
         # kernel covers every axis: dense attention over the extent (functional.py:141-143, 271)
         ca = (2,) * rank
-    if add_k is not None and query.is_cuda and query.dtype in (torch.float16, torch.bfloat16) \
-            and query.shape[-1] in (32, 64, 128) and all(s == 1 for s in st):
-        # shapes the tensor-core kernels take: the neighbourhood branch runs there, the extra tokens
-        # as in the reference's composition (functional.py:340-381): dense attention + merge
-        out, lse = _ag.fused_with_grad(query, key, value, ks, st, dl, ca, scale_value)
-        q_flat = query.reshape(query.shape[0], -1, query.shape[-2], query.shape[-1])
-        out_x, lse_x = _ag.dense_extra_with_grad(q_flat, add_k, add_v, scale_value)
-        out, lse = _ag.merge_pair_with_grad(out, lse, out_x.reshape(out.shape), lse_x.reshape(lse.shape))
-        return (out, lse) if return_lse else out
     out, lse = _ag.fused_with_grad(query, key, value, ks, st, dl, ca, scale_value, add_k, add_v)
     return (out, lse) if return_lse else out
 
@@ -200,7 +196,8 @@ def na3d_av(attn, value, kernel_size, dilation=1, *, stride=1, is_causal=False):
 
 def _validate_sizes(sizes, batch, max_spatial, ks, rank, host_sizes=None):
     """Checks of functional.py:637-694.  ``sizes`` may live on the GPU; the
-    range checks read ``host_sizes`` when given, else copy ``sizes`` to the host."""
+    range checks read ``host_sizes`` when given, else copy ``sizes`` to the host.
+    Returns the sizes tensor and the host list of per-sample extents."""
     if not torch.is_tensor(sizes):
         sizes = torch.as_tensor(sizes)
     if rank == 1:
@@ -228,7 +225,7 @@ def _validate_sizes(sizes, batch, max_spatial, ks, rank, host_sizes=None):
             if hi > max_spatial[a]:
                 raise ValueError(
                     f"All spatial_sizes[:,{a}] must be <= max_spatial[{a}] ({max_spatial[a]}), but max={hi}.")
-    return sizes
+    return sizes, [tuple(int(x) for x in row) for row in host.tolist()]
 
 
 def _varlen(rank, query, key, value, sizes, kernel_size, dilation, scale, return_lse, additional_keys,
@@ -246,46 +243,12 @@ def _varlen(rank, query, key, value, sizes, kernel_size, dilation, scale, return
     for a, d in enumerate(dl):
         if not isinstance(d, int) or d <= 0:
             raise ValueError(f"dilation[{a}] must be a positive int, got {d!r}")
-    sizes = _validate_sizes(sizes, query.shape[0], tuple(query.shape[1:-2]), ks, rank, host_sizes)
+    sizes, host = _validate_sizes(sizes, query.shape[0], tuple(query.shape[1:-2]), ks, rank, host_sizes)
     scale_value = query.shape[-1] ** -0.5 if scale is None else float(scale)
     one, no = (1,) * rank, (False,) * rank
-    from ._core import cuda as _backend
-    if query.is_cuda and query.dtype in (torch.float16, torch.bfloat16):
-        host = host_sizes if host_sizes is not None else sizes.detach().cpu().tolist()
-        host = [tuple(int(x) for x in (s if isinstance(s, (list, tuple)) else (s,))) for s in host]
-        if _backend.per_sample_tensor_core_ok(query, key, host, ks, dl, scale_value):
-            out, lse = _varlen_tensor_core(rank, query, key, value, host, ks, dl, scale_value, add_k, add_v)
-            return (out, lse) if return_lse else out
     out, lse = _ag.fused_with_grad(query, key, value, ks, one, dl, no, scale_value, add_k, add_v,
-                                   sizes.to(device=query.device, dtype=torch.int32))
+                                   sizes.to(device=query.device, dtype=torch.int32), host)
     return (out, lse) if return_lse else out
-
-
-def _varlen_tensor_core(rank, query, key, value, host, ks, dl, scale_value, add_k, add_v):
-    """Variable-size batch on the tensor-core kernels: one call per sample for the neighbourhood
-    branch; extra tokens as the reference composes them (functional.py:340-381): dense attention
-    over the extra tokens (the library's scaled-dot-product kernel, as the reference's
-    ``mx.fast.scaled_dot_product_attention``) merged with the neighbourhood branch through the
-    log-sum-exps by the merge kernel."""
-    out, lse = _ag.per_sample_with_grad(query, key, value, host, ks, dl, scale_value)
-    if add_k is None:
-        return out, lse
-    batch, heads_q, dim = query.shape[0], query.shape[-2], query.shape[-1]
-    spatial = tuple(query.shape[1:1 + rank])
-    # rows inside each sample's extents (padding may hold anything: it is replaced by zeros before the product)
-    mask = torch.ones((batch,) + spatial, dtype=torch.bool, device=query.device)
-    for a in range(rank):
-        idx = torch.arange(spatial[a], device=query.device).view((1,) + (1,) * a + (-1,) + (1,) * (rank - 1 - a))
-        lim = torch.tensor([s[a] for s in host], device=query.device).view((batch,) + (1,) * rank)
-        mask = mask & (idx < lim)
-    q_in = torch.where(mask[..., None, None], query, torch.zeros((), dtype=query.dtype, device=query.device))
-    q_in = q_in.reshape(batch, -1, heads_q, dim)
-    out_x, lse_x = _ag.dense_extra_with_grad(q_in, add_k, add_v, scale_value)   # head dim is 32, 64 or 128 here
-    out_x = out_x.reshape(query.shape)
-    lse_x = lse_x.reshape(query.shape[:-1])
-    out_m, lse_m = _ag.merge_pair_with_grad(out, lse, out_x, lse_x)
-    keep = mask[..., None]
-    return out_m * keep[..., None].to(out_m.dtype), lse_m * keep.to(lse_m.dtype)
 
 
 def na1d_varlen(query, key, value, seq_lens, kernel_size, dilation=1, scale: Optional[float] = None, *,

@@ -29,13 +29,13 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} is declared in the header but not exported"
     assert declared == set(_lib.SYMBOLS), "ctypes table and header disagree"
-    assert _lib.load().natten_b200_abi_version() == 1
+    assert _lib.load().natten_b200_abi_version() == 2
 
 
 def test_geom_struct_layout_matches_header():
     # the C side pins the same numbers with static_assert (csrc/api.cu)
-    assert ctypes.sizeof(_lib.Geom) == 168
-    assert _lib.Geom.extents.offset == 144 and _lib.Geom.scale.offset == 132
+    assert ctypes.sizeof(_lib.Geom) == 176
+    assert _lib.Geom.extents.offset == 144 and _lib.Geom.scale.offset == 132 and _lib.Geom.host_extents.offset == 168
 
 
 def test_axis_table_matches_reference_tables_bit_exact():

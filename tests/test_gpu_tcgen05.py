@@ -1,7 +1,7 @@
 """The tensor-core (tcgen05 / TMEM / TMA) fused kernels against the CPU oracle
 and against the CUDA-core kernels, through the C ABI with the kernel family
 forced.  bf16 / fp16 tolerance against the float32 oracle: 2e-2 of the largest reference
-magnitude and 2e-2 per element (|err| <= 2e-2 * (|ref| + rms(ref)))."""
+magnitude and 4e-2 per element (|err| <= 4e-2 * (|ref| + rms(ref)))."""
 
 from __future__ import annotations
 

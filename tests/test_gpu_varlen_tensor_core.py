@@ -1,5 +1,6 @@
-"""Variable-size batches on the tensor-core kernels: one call per sample with the sample handed
-over as the leading corner of its padded block (``mem_extent`` of the C geometry).
+"""Variable-size batches and extra tokens on the tensor-core kernels: one launch per kernel for the whole
+batch (every sample has TMA tensor maps with its own bounds; tiles outside a sample are skipped), the extra
+tokens as one more chunk of keys of the same softmax and as extra work items of the dK/dV kernel.
 
 Padding is filled with NaN on purpose: the reference slices every sample out of the padded
 tensors (src/natten_mlx/_core/pure.py:559-577), so nothing outside a sample's extents may reach
@@ -54,7 +55,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("shape,hkv,sizes,ks,dl,n_extra", CASES)
-def test_per_sample_tensor_core_varlen(shape, hkv, sizes, ks, dl, n_extra):
+def test_tensor_core_varlen_one_launch_per_kernel(shape, hkv, sizes, ks, dl, n_extra):
     rank = len(shape) - 3
     dt = torch.bfloat16
     kv_shape = shape[:-2] + (hkv, shape[-1])
@@ -76,11 +77,16 @@ def test_per_sample_tensor_core_varlen(shape, hkv, sizes, ks, dl, n_extra):
     fn = {1: nb.na1d_varlen, 2: nb.na2d_varlen, 3: nb.na3d_varlen}[rank]
     dev_ins = [_poison(t, sizes).to(DEV).requires_grad_(True) for t in ins[:3]] + \
               [t.to(DEV).requires_grad_(True) for t in ins[3:]]
+    n0 = _lib.launch_count()
     out, lse = fn(dev_ins[0], dev_ins[1], dev_ins[2], st, ks if rank > 1 else ks[0], dl if rank > 1 else dl[0],
                   return_lse=True, additional_keys=dev_ins[3] if n_extra else None,
                   additional_values=dev_ins[4] if n_extra else None, host_sizes=sz)
     assert _lib.last_path() == "tcgen05" and _lib.kernel_status() == 0
+    n1 = _lib.launch_count()
+    assert n1 - n0 == 1, "the forward of a variable-size batch is one launch"
     grads = torch.autograd.grad((out, lse), dev_ins, (_poison(cot, sizes).to(DEV).nan_to_num(0.0), cot_l.to(DEV)))
+    # pre-pass, dQ, dK/dV (+ one cast of the extra-token accumulators)
+    assert _lib.launch_count() - n1 == (4 if n_extra else 3) and _lib.kernel_status() == 0
     _close(out, o_ref, "out")
     _close(lse, l_ref, "lse")
     for name, a, b in zip(("dq", "dk", "dv", "dak", "dav"), grads, g_ref):
@@ -114,11 +120,13 @@ def test_mem_extent_is_refused_where_it_does_not_apply():
 @pytest.mark.parametrize("shape,hkv,ks,dl,ca,n_extra", [
     ((2, 20, 24, 4, 64), 2, (7, 5), (1, 2), (False, False), 6),
     ((1, 40, 2, 32), 2, (9,), (1,), (True,), 3),
+    ((1, 12, 14, 8, 32), 2, (5, 5), (1, 1), (False, False), 150),      # more extra tokens than a tile of 128 rows
+    ((2, 4, 10, 12, 2, 64), 1, (3, 5, 3), (1, 1, 2), (True, False, False), 20),
 ])
-def test_extra_tokens_composed_on_the_tensor_core_path(shape, hkv, ks, dl, ca, n_extra):
-    """Dense (not variable-size) call with extra tokens in bf16: neighbourhood branch on the tensor-core
-    kernels, extra tokens by dense attention, merged through the log-sum-exps; out, lse and all gradients
-    (including the one that flows through the returned lse) against the oracle."""
+def test_extra_tokens_inside_the_tensor_core_kernels(shape, hkv, ks, dl, ca, n_extra):
+    """Dense (not variable-size) call with extra tokens in bf16: window and extra tokens share the softmax of
+    the tensor-core kernels; out, lse and all gradients (including the one that flows through the returned
+    lse) against the oracle."""
     rank = len(shape) - 3
     dt = torch.bfloat16
     kv_shape = shape[:-2] + (hkv, shape[-1])
@@ -130,9 +138,10 @@ def test_extra_tokens_composed_on_the_tensor_core_path(shape, hkv, ks, dl, ca, n
     (o_ref, l_ref), g_ref = oracle.grads(ref, [t.float() for t in ins], (cot.float(), cot_l))
     fn = {1: nb.na1d, 2: nb.na2d, 3: nb.na3d}[rank]
     dev_ins = [t.to(DEV).requires_grad_(True) for t in ins]
+    n0 = _lib.launch_count()
     out, lse = fn(dev_ins[0], dev_ins[1], dev_ins[2], kernel_size=ks, dilation=dl, is_causal=ca, return_lse=True,
                   additional_keys=dev_ins[3], additional_values=dev_ins[4])
-    assert _lib.last_path() == "tcgen05"
+    assert _lib.last_path() == "tcgen05" and _lib.launch_count() - n0 == 1
     grads = torch.autograd.grad((out, lse), dev_ins, (cot.to(DEV), cot_l.to(DEV)))
     _close(out, o_ref, "out")
     _close(lse, l_ref, "lse")
