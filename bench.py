@@ -14,9 +14,12 @@ buffers, host<->device copies inside the timed region.  ``roofline`` is for
 the kernel with the largest share of device time, measured live with CUDA
 events recorded by the library around each of its launches.
 
-With ``--gpus N`` (launched by torchrun, one rank per GPU) every rank runs the
-same per-GPU batch (weak scaling, no data-path collective: the batch x head
-shards are independent); time is the max over ranks.
+With ``--gpus N`` (launched by torchrun, one rank per GPU) the named batch is
+sharded over the ranks (32 / N samples each: strong scaling, no data-path
+collective, the batch x head shards are independent); time is the max over
+ranks.  The line also carries the weak-scaling figure (every rank the whole
+batch) and, under ``na3d_video``, the video volume sharded by heads and sharded
+along T with the K/V halo exchange over NCCL.
 
 ``--impl reference`` times the CPU restatement of the reference's pure backend
 (the MLX array library it needs does not install on Linux) on the host cores.
@@ -230,18 +233,66 @@ def run_reference(args, w, rank, world):
 # ---------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------
+def shard_batch(total, world, rank):
+    """Samples [lo, hi) of a batch of `total` that rank `rank` of `world` owns (balanced contiguous split)."""
+    return (total * rank) // world, (total * (rank + 1)) // world
+
+
+class FusedRunner:
+    """Device-resident fused forward + backward calls of one workload on this rank's shard, replayed from a CUDA graph
+    (the launches of a step are a fixed sequence; at small per-GPU batches the host would otherwise be the limit)."""
+
+    def __init__(self, w, dev, seed0=1234):
+        from natten_mlx_b200._core import cuda as backend
+        self.w, self.dev, self.backend = w, dev, backend
+        self.one = (1,) * (len(w["shape"]) - 3)
+        self.inputs = [make_inputs(w, seed0 + vi, dev) for vi in range(len(w["dilations"]))]
+        self.graph = None
+
+    def step_eager(self):
+        w, be = self.w, self.backend
+        res = None
+        for (q, k, v, cot), dil in zip(self.inputs, w["dilations"]):
+            out, lse = be.fused_forward(q, k, v, w["kernel"], self.one, dil, w["causal"], None)
+            res = be.fused_backward(q, k, v, out, lse, cot, None, w["kernel"], self.one, dil, w["causal"], None)
+        return res
+
+    def capture(self):
+        """Returns True when the step now replays from a graph (eager launches otherwise)."""
+        try:
+            side = torch.cuda.Stream(device=self.dev)
+            side.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self.step_eager()
+            torch.cuda.current_stream(self.dev).wait_stream(side)
+            torch.cuda.synchronize(self.dev)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._keep = self.step_eager()
+            self.graph = graph
+        except Exception:                      # capture is an optimisation of the launch path, never a requirement
+            self.graph = None
+            torch.cuda.synchronize(self.dev)
+        return self.graph is not None
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_eager()
+
+
 def run_ours(args, w, rank, world, local_rank):
     import torch.distributed as dist
     import natten_mlx_b200 as nb
     from natten_mlx_b200 import _lib
-    from natten_mlx_b200._core import cuda as backend
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device for the default arm (there is no CPU path)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    rank_nd = len(w["shape"]) - 3
-    one, nvar = (1,) * rank_nd, len(w["dilations"])
+    nvar = len(w["dilations"])
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
@@ -250,38 +301,16 @@ def run_ours(args, w, rank, world, local_rank):
         pass
     hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
     peak_kind = "measured" if "hbm_gbs" in peaks else "fallback"
-
-    # device-resident inputs, one set per variant so that no variant finds its inputs in L2
-    dev_in = [make_inputs(w, 1234 + vi, dev) for vi in range(nvar)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
-    def step_device():
-        for (q, k, v, cot), dil in zip(dev_in, w["dilations"]):
-            out, lse = backend.fused_forward(q, k, v, w["kernel"], one, dil, w["causal"], None)
-            backend.fused_backward(q, k, v, out, lse, cot, None, w["kernel"], one, dil, w["causal"], None)
-
-    # end-to-end: pinned host buffers -> device -> public API forward + backward -> host
-    host_in = [make_inputs(w, 1234 + vi, dev, pinned=True) for vi in range(nvar)]
-    host_out = [[torch.empty_like(t).pin_memory() for t in (hi[0], hi[0], hi[1], hi[2])] for hi in host_in]
-    h2d = sum(t.numel() * t.element_size() for hi in host_in for t in hi)
-    d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
-
-    # one streaming plan per variant: batch slabs travel in, are computed and travel out concurrently
-    from natten_mlx_b200.host import HostPipeline
-    pipes = [HostPipeline(w["shape"], host_in[0][0].dtype, dev, w["kernel"], dilation=dil, is_causal=w["causal"],
-                          heads_kv=w["heads_kv"], slabs=8) for dil in w["dilations"]]
-
-    def step_e2e():
-        for hi, ho, pipe in zip(host_in, host_out, pipes):      # the variants share the streams and keep streaming
-            pipe.run(hi[0], hi[1], hi[2], hi[3], ho[0], ho[1], ho[2], ho[3], wait=False)
-        pipes[-1].join()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(step_fn, steps, trace):
+    def timed(step_fn, steps, trace=False):
+        """Mean device milliseconds per step: CUDA events around every step, L2 flushed before each, barrier +
+        synchronize on both sides, maximum over the ranks."""
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
         barrier()
         if trace:
@@ -302,36 +331,74 @@ def run_ours(args, w, rank, world, local_rank):
             ms = float(t.item())
         return ms / steps
 
-    # measured tiling per variant (the library's tuning entry point; part of the warm-up, recorded in `config`)
+    # ---- the workload: the named batch sharded over the ranks (strong scaling; at one GPU the whole batch)
+    B = w["shape"][0]
+    lo, hi = shard_batch(B, world, rank)
+    w_loc = dict(w, shape=(hi - lo,) + tuple(w["shape"][1:]))
+    main = FusedRunner(w_loc, dev, seed0=1234 + 16 * rank)
     tuned = {}
-    for (q, k, v, cot), dil in zip(dev_in, w["dilations"] if not args.no_tune else []):
+    for (q, k, v, cot), dil in zip(main.inputs, w["dilations"] if not args.no_tune else []):
         res = nb.tune.tune_fused(q, k, v, w["kernel"], dilation=dil, is_causal=w["causal"])
         tuned["x".join(str(d) for d in dil)] = {kn: {"tile": list(t), "max_cols": c} for kn, (t, c, _) in res.items()}
     for _ in range(max(args.warmup, 3)):
-        step_device()
+        main.step_eager()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches0 = _lib.launch_count()
-    ms_dev = timed(step_device, args.steps, trace=True)
+    ms_trace = timed(main.step_eager, args.steps, trace=True)      # eager launches with per-kernel events
     launches = _lib.launch_count() - launches0
     trace = _lib.trace_report()
     path = _lib.last_path()
+    ms_eager = timed(main.step_eager, args.steps)
+    graphed = main.capture()
+    for _ in range(3):
+        main.step()
+    ms_plain = timed(main.step, args.steps)                        # the headline: same launches, replayed
+
+    # ---- end to end: pinned host buffers -> device -> public API forward + backward -> host, on the same shard
+    host_in = [make_inputs(w_loc, 1234 + 16 * rank + vi, dev, pinned=True) for vi in range(nvar)]
+    host_out = [[torch.empty_like(t).pin_memory() for t in (hi_[0], hi_[0], hi_[1], hi_[2])] for hi_ in host_in]
+    h2d = sum(t.numel() * t.element_size() for hi_ in host_in for t in hi_)
+    d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
+    from natten_mlx_b200.host import HostPipeline
+    pipes = [HostPipeline(w_loc["shape"], host_in[0][0].dtype, dev, w["kernel"], dilation=dil, is_causal=w["causal"],
+                          heads_kv=w["heads_kv"], slabs=8) for dil in w["dilations"]]
+
+    def step_e2e():
+        for hi_, ho, pipe in zip(host_in, host_out, pipes):     # the variants share the streams and keep streaming
+            pipe.run(hi_[0], hi_[1], hi_[2], hi_[3], ho[0], ho[1], ho[2], ho[3], wait=False)
+        pipes[-1].join()
+
     for _ in range(2):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps, trace=False)
+    ms_e2e = timed(step_e2e, args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
-    # the traced timings include the event overhead, so recompute ms_dev untraced as the headline
-    ms_plain = timed(step_device, args.steps, trace=False)
+    # ---- weak scaling for the record (every rank the whole named batch): N > 1 only
+    weak = None
+    if world > 1:
+        wk = FusedRunner(w, dev, seed0=2234 + 16 * rank)
+        for _ in range(3):
+            wk.step_eager()
+        wk.capture()
+        for _ in range(2):
+            wk.step()
+        ms_weak = timed(wk.step, args.steps)
+        weak = {"ms_per_step": ms_weak, "value": flops_step(w) * world / (ms_weak * 1e-3) / 1e12, "per_gpu_batch": B,
+                "global_batch": B * world}
+        del wk
+
+    # ---- the video volume on the same ranks: sharded by heads (no collective) and along T (K/V halo exchange)
+    video = run_video_legs(args, rank, world, dev, timed, barrier) if args.workload == "na2d_nat_stage" else None
 
     if rank != 0:
         return
-    total_flops = flops_step(w) * world
+    total_flops = flops_step(w)                    # the named batch, whatever the number of ranks
     value = total_flops / (ms_plain * 1e-3) / 1e12
     e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
 
-    alg = algorithmic_bytes(w)
+    alg = algorithmic_bytes(w_loc)
     roofline = None
     if trace:
         name, (n, ms_total) = max(trace.items(), key=lambda kv: kv[1][1])
@@ -339,10 +406,11 @@ def run_ours(args, w, rank, world, local_rank):
         share = ms_total / sum(v[1] for v in trace.values())
         if name in alg:
             achieved = alg[name] / (per_launch_ms * 1e-3) / 1e9
+            traffic = NCU_TRAFFIC.get(args.workload, {}).get(name)
             roofline = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                        "frac": achieved / hbm_peak, "traffic": NCU_TRAFFIC.get(args.workload, {}).get(name),
-                        "peak_kind": peak_kind,
-                        "launch_ms": per_launch_ms, "share_of_device_time": share,
+                        "frac": achieved / hbm_peak,
+                        "traffic": traffic * (hi - lo) / B if traffic is not None else None,   # scales with the batch
+                        "peak_kind": peak_kind, "launch_ms": per_launch_ms, "share_of_device_time": share,
                         "algorithmic_bytes_per_launch": alg[name]}
     kernels = {k: {"launches": n, "ms_per_launch": ms / n} for k, (n, ms) in sorted(trace.items())}
 
@@ -358,30 +426,113 @@ def run_ours(args, w, rank, world, local_rank):
         cpu_tflops = flops_step(cpu_sample_workload(w, batch)) * reps / t_cpu / 1e12
         cpu = {"value": cpu_tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                "sample": f"shape {cpu_sample_workload(w, batch)['shape']} of {w['shape']}, {reps} repetitions, float32 "
-                         "CPU restatement of the reference's pure backend, forward+backward of every variant"}
+                         "CPU restatement of the reference's pure backend, forward+backward of every variant",
+               "mlx_core_importable": mlx_importable()}
 
     line = {
         "metric": "na_fwd_bwd_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_plain, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-        "config": {"workload": w["label"], "calls_per_step": nvar, "per_gpu_batch": w["shape"][0],
-                   "global_batch": w["shape"][0] * world, "parallelism": f"batch-sharded x{world}, no collective",
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": w["label"], "calls_per_step": nvar, "per_gpu_batch": hi - lo,
+                   "global_batch": B, "parallelism": f"batch of {B} sharded over {world} rank(s), no collective",
                    "l2": "256 MiB buffer written between timed iterations; separate inputs per variant",
                    "kernel_family": path, "flops_model": "fwd 4*B*H*N*K_vol*D, bwd 2.5x fwd",
+                   "launch": "CUDA graph replay of the step's launches" if graphed else "eager launches",
+                   "ms_per_step_eager": ms_eager, "ms_per_step_eager_traced": ms_trace,
                    "ms_per_call_fwd_bwd": ms_plain / nvar,
                    "tuned_plans": tuned},
         "roofline": roofline, "kernels": kernels, "cpu_baseline": cpu,
-        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": d2h * world,
+                "per_rank": {"h2d_gb_per_s": h2d / (ms_e2e * 1e-3) / 1e9, "d2h_gb_per_s": d2h / (ms_e2e * 1e-3) / 1e9,
+                             "note": "rank 0's bytes over the step time (max over ranks); the two directions overlap"}},
         "gpu_launches": int(launches), "clocks": clocks,
     }
+    if weak is not None:
+        line["weak_scaling"] = weak
+    if video is not None:
+        line["na3d_video"] = video
     print(json.dumps(line))
 
 
+def mlx_importable():
+    """Whether the array library of the reference is importable here (it is not on Linux images; when it is, the
+    fixtures under tests/golden can be regenerated against it with tests/golden/make_golden.py)."""
+    try:
+        import importlib.util
+        return importlib.util.find_spec("mlx.core") is not None
+    except (ImportError, ValueError):
+        return False
+
+
+def run_video_legs(args, rank, world, dev, timed, barrier):
+    """The 3-D video volume (bf16 B=2 T=32 96x96 16 heads D=64, kernel (3,7,7), causal along T, dilation (1,2,2)) on
+    the same ranks, as extra figures of the line: the heads sharded over the ranks (no collective) and the volume
+    sharded along T with the K/V halo exchange.  Forward + backward per step; returns rank 0's summary."""
+    import torch.distributed as dist
+    import natten_mlx_b200 as nb
+    from natten_mlx_b200 import _lib, sharding
+
+    w = WORKLOADS["na3d_video"]
+    steps = max(3, min(args.steps, 5))
+    out = {"workload": w["label"], "steps": steps}
+    heads = w["shape"][-2]
+
+    def traced(step_fn):
+        for _ in range(2):
+            step_fn()
+        ms = timed(step_fn, steps, trace=True)
+        kernels = {k: {"launches": n, "ms_per_launch": t / n} for k, (n, t) in sorted(_lib.trace_report().items())}
+        ksum = sum(v["ms_per_launch"] * v["launches"] for v in kernels.values()) / steps
+        return ms, kernels, ksum
+
+    # (a) heads sharded: every rank the whole volume for heads [lo, hi)
+    if heads % world == 0:
+        hloc = heads // world
+        w_h = dict(w, shape=tuple(w["shape"][:-2]) + (hloc, w["shape"][-1]), heads_kv=hloc)
+        r = FusedRunner(w_h, dev, seed0=3234 + 16 * rank)
+        ms, kernels, ksum = traced(r.step_eager)
+        out["heads_sharded"] = {"ms_per_step": ms, "heads_per_gpu": hloc, "value": flops_step(w) / (ms * 1e-3) / 1e12,
+                                "kernels_rank0": kernels, "kernel_ms_per_step_rank0": ksum}
+        del r
+        torch.cuda.empty_cache()
+    # (b) sharded along T: K/V halo planes by point-to-point send/recv (NCCL)
+    B, T = w["shape"][0], w["shape"][1]
+    if world <= T:
+        bounds = sharding.shard_bounds(T, world)
+        lo, hi = bounds[rank], bounds[rank + 1]
+        gen = torch.Generator().manual_seed(1240 + rank)
+        local = (B, hi - lo) + tuple(w["shape"][2:])
+        ks, dl, ca = w["kernel"], w["dilations"][0], w["causal"]
+        plans = sharding.all_plans(T, world, ks[0], dl[0], ca[0])
+        mk = lambda: torch.randn(local, generator=gen, dtype=torch.float32).to(torch.bfloat16).to(dev)
+        q, cot = mk().requires_grad_(True), mk()
+        # K and V live in buffers with room for the halo planes: the exchange receives straight into them
+        kb, k = sharding.halo_buffer(q.detach(), plans, rank)
+        vb, v = sharding.halo_buffer(q.detach(), plans, rank)
+        k.copy_(mk())
+        v.copy_(mk())
+        k.requires_grad_(True)
+        v.requires_grad_(True)
+
+        def step():
+            o = nb.na3d(q, k, v, kernel_size=ks, dilation=dl, is_causal=ca) if world == 1 else \
+                sharding.na_sharded(q, k, v, T, ks, dl, ca)
+            return torch.autograd.grad(o, (q, k, v), cot)
+        ms, kernels, ksum = traced(step)
+        out["t_sharded"] = {"ms_per_step": ms, "planes_per_rank": [bounds[r + 1] - bounds[r] for r in range(world)],
+                            "value": flops_step(w) / (ms * 1e-3) / 1e12, "kernels_rank0": kernels,
+                            "kernel_ms_per_step_rank0": ksum,
+                            "halo": "K/V planes received straight into the halo planes of the K/V buffers; dK/dV partials "
+                                    "of the halo planes sent back and added in place"}
+    return out
+
+
 # ---------------------------------------------------------------------------
-# table workloads (BASELINE configs 3 and 5): device-resident, single GPU, no CPU or end-to-end leg
+# table workloads (the allin1 split 1-D path and the variable-size GQA batch with extra tokens): device-resident,
+# single GPU, no CPU or end-to-end leg
 # ---------------------------------------------------------------------------
-TABLE_WORKLOADS = ("allin1_1d", "na2d_varlen_gqa")
+TABLE_WORKLOADS = ("allin1_1d", "allin1_1d_long", "na2d_varlen_gqa")
 
 
 def run_table_workload(args):
@@ -393,15 +544,20 @@ def run_table_workload(args):
     torch.cuda.set_device(dev)
     gen = torch.Generator().manual_seed(1236)
     rnd = lambda shape, dt: torch.randn(shape, generator=gen, dtype=torch.float32).to(dt).to(dev)
-    if args.workload == "allin1_1d":
-        # q, k, v [8,4096,4,12] fp32, rpb [4,9] ~ N(0,0.02), K=5, dilation 2, scale 0.288: QK+RPB -> softmax -> AV
-        q, k, v = (rnd((8, 4096, 4, 12), torch.float32) for _ in range(3))
+    kernel_bytes = None
+    if args.workload in ("allin1_1d", "allin1_1d_long"):
+        # q, k, v [8,L,4,12] fp32, rpb [4,9] ~ N(0,0.02), K=5, dilation 2, scale 0.288: QK+RPB -> softmax -> AV
+        # (L = 4096 is the named configuration; the long variant, 16 times the length, takes launch latency out
+        # of the per-kernel bandwidth figures)
+        L = 4096 if args.workload == "allin1_1d" else 65536
+        q, k, v = (rnd((8, L, 4, 12), torch.float32) for _ in range(3))
         rpb = rnd((4, 9), torch.float32) * 0.02
-        label = "allin1 fp32 na1d_qk_rpb -> softmax -> na1d_av_fused, B=8 L=4096 H=4 D=12 K=5 dilation 2"
-        tens = 8 * 4096 * 4 * 12 * 4
-        logit = 8 * 4096 * 4 * 5 * 4
+        label = f"allin1 fp32 na1d_qk_rpb -> softmax -> na1d_av_fused, B=8 L={L} H=4 D=12 K=5 dilation 2"
+        tens = 8 * L * 4 * 12 * 4
+        logit = 8 * L * 4 * 5 * 4
         byts = (2 * tens + logit) + 2 * logit + (logit + 2 * tens)       # QK ; softmax ; AV
-        flops = 2 * 4.0 * 8 * 4 * 4096 * 5 * 12 / 2                      # 2*N*K*D for QK and again for AV
+        kernel_bytes = {"row_dot": 2 * tens + logit, "row_wsum": logit + 2 * tens}
+        flops = 2 * 4.0 * 8 * 4 * L * 5 * 12 / 2                         # 2*N*K*D for QK and again for AV
 
         def eager():
             with torch.no_grad():
@@ -472,6 +628,22 @@ def run_table_workload(args):
             peaks = json.load(fh)
     except OSError:
         pass
+    # per-kernel device time of the library's launches (eager launches bracketed by events)
+    run_eager = eager if eager is not None else step
+    _lib.trace_report()
+    _lib.trace_enable(True)
+    for _ in range(args.steps):
+        flush.zero_()
+        run_eager()
+    torch.cuda.synchronize()
+    _lib.trace_enable(False)
+    kernels = {}
+    for name, (n, ms_total) in sorted(_lib.trace_report().items()):
+        kernels[name] = {"launches_per_step": n / args.steps, "ms_per_launch": ms_total / n}
+        if kernel_bytes is not None and name in kernel_bytes:
+            gbs = kernel_bytes[name] / (ms_total / n * 1e-3) / 1e9
+            kernels[name].update(algorithmic_bytes=kernel_bytes[name], gb_per_s=gbs,
+                                 frac_of_hbm_peak=gbs / float(peaks.get("hbm_gbs", 6650.0)))
     roofline = None
     if byts is not None:
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
@@ -485,11 +657,12 @@ def run_table_workload(args):
         "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
         "config": dict({"workload": label, "l2": "256 MiB buffer written between timed iterations",
                         "kernel_family": _lib.last_path()}, **extra_cfg),
-        "roofline": roofline, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}))
+        "roofline": roofline, "kernels": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches),
+        "clocks": clocks}))
 
 
 # ---------------------------------------------------------------------------
-# BASELINE config 4 sharded along T over the ranks (strong scaling, K/V halo exchange over NCCL)
+# the video volume sharded along T over the ranks (strong scaling, K/V halo exchange over NCCL)
 # ---------------------------------------------------------------------------
 def run_tshard(args, rank, world, local_rank):
     import torch.distributed as dist

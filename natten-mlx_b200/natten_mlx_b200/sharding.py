@@ -65,65 +65,108 @@ def _overlap(a_lo, a_hi, b_lo, b_hi) -> Tuple[int, int]:
     return (lo, hi) if hi > lo else (0, 0)
 
 
-def exchange_halo(local: torch.Tensor, plans: Sequence[SlabPlan], rank: int, group=None, axis: int = 1) -> torch.Tensor:
-    """Return the K (or V) buffer covering planes [kv_lo, kv_hi) of this rank.
+def _planes(t: torch.Tensor, axis: int, lo: int, n: int):
+    """Planes [lo, lo + n) of ``t`` along ``axis`` as dense pieces, one per leading index (point-to-point
+    transfers need dense tensors).  The split depends on the shape alone, never on whether a particular
+    slice happens to be dense, so that sender and receiver always agree on the number of pieces."""
+    piece = t.narrow(axis, lo, n)
+    lead = list(t.shape[:axis])
+    count = 1
+    for x in lead:
+        count *= x
+    if count == 1:
+        return [piece.reshape(piece.shape[axis:]) if piece.is_contiguous() else piece.contiguous()]
+    flat = piece.reshape([count] + list(piece.shape[axis:])) if len(lead) == 1 else None
+    if flat is not None:
+        return [flat[i] for i in range(count)]
+    out = []
+    for idx in torch.cartesian_prod(*[torch.arange(x) for x in lead]).reshape(-1, len(lead)).tolist():
+        out.append(piece[tuple(idx)])
+    return out
 
-    ``local`` holds the owned planes [q_lo, q_hi) along ``axis``.  Planes owned
-    by other ranks arrive by point-to-point receives; this rank sends the
-    planes others need.  All ranks must call this in the same order.
-    """
+
+def halo_buffer(local: torch.Tensor, plans: Sequence[SlabPlan], rank: int, axis: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(buffer over planes [kv_lo, kv_hi), its view of the owned planes [q_lo, q_hi)).  A caller that produces
+    its K/V directly into the view saves ``exchange_halo`` the copy of the owned planes."""
     me = plans[rank]
     shape = list(local.shape)
     shape[axis] = me.kv_hi - me.kv_lo
     buf = local.new_empty(shape)
-    buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo).copy_(local)
-    ops, keep = [], []
+    return buf, buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo)
+
+
+def _is_view_of_own_planes(local: torch.Tensor, me: SlabPlan, axis: int) -> Optional[torch.Tensor]:
+    """The halo buffer ``local`` is the owned-planes view of (see ``halo_buffer``), or None."""
+    base = local._base
+    if base is None or base.dim() != local.dim() or not base.is_contiguous():
+        return None
+    want = list(local.shape)
+    want[axis] = me.kv_hi - me.kv_lo
+    if list(base.shape) != want or local.stride() != base.stride():
+        return None
+    if local.storage_offset() - base.storage_offset() != (me.q_lo - me.kv_lo) * base.stride(axis):
+        return None
+    return base
+
+
+def exchange_halo(local: torch.Tensor, plans: Sequence[SlabPlan], rank: int, group=None, axis: int = 1) -> torch.Tensor:
+    """Return the K (or V) buffer covering planes [kv_lo, kv_hi) of this rank.
+
+    ``local`` holds the owned planes [q_lo, q_hi) along ``axis``.  Planes owned by other ranks are received
+    straight into their place in the buffer; this rank sends the planes others need straight from ``local``
+    (no staging copies: transfers go plane range by plane range, per leading index where a range is not
+    dense).  When ``local`` already is the owned-planes view of a ``halo_buffer`` nothing is copied at all.
+    All ranks must call this in the same order.
+    """
+    me = plans[rank]
+    if me.kv_lo == me.q_lo and me.kv_hi == me.q_hi:
+        buf = local if local.is_contiguous() else local.contiguous()       # this rank borrows nothing (it may still lend)
+        local = buf
+    else:
+        buf = _is_view_of_own_planes(local, me, axis)
+        if buf is None:
+            buf, own = halo_buffer(local, plans, rank, axis)
+            own.copy_(local)
+    ops = []
     for other in plans:
         if other.rank == rank:
             continue
         lo, hi = _overlap(me.q_lo, me.q_hi, other.kv_lo, other.kv_hi)       # what `other` needs from me
         if hi > lo:
-            piece = local.narrow(axis, lo - me.q_lo, hi - lo).contiguous()
-            keep.append(piece)
-            ops.append(dist.P2POp(dist.isend, piece, _global_rank(other.rank, group), group))
+            for piece in _planes(local, axis, lo - me.q_lo, hi - lo):
+                ops.append(dist.P2POp(dist.isend, piece, _global_rank(other.rank, group), group))
         lo, hi = _overlap(other.q_lo, other.q_hi, me.kv_lo, me.kv_hi)       # what I need from `other`
         if hi > lo:
-            piece = local.new_empty(shape[:axis] + [hi - lo] + shape[axis + 1:])
-            keep.append((piece, lo, hi))
-            ops.append(dist.P2POp(dist.irecv, piece, _global_rank(other.rank, group), group))
+            for piece in _planes(buf, axis, lo - me.kv_lo, hi - lo):
+                ops.append(dist.P2POp(dist.irecv, piece, _global_rank(other.rank, group), group))
     if ops:
         for req in dist.batch_isend_irecv(ops):
             req.wait()
-    for item in keep:
-        if isinstance(item, tuple):
-            piece, lo, hi = item
-            buf.narrow(axis, lo - me.kv_lo, hi - lo).copy_(piece)
     return buf
 
 
 def reduce_halo_grads(grad_buf: torch.Tensor, plans: Sequence[SlabPlan], rank: int, group=None, axis: int = 1) -> torch.Tensor:
-    """Inverse of ``exchange_halo`` for gradients: ``grad_buf`` covers planes
-    [kv_lo, kv_hi); partial sums for planes owned elsewhere are sent to their
-    owners and the owner adds what it receives.  Returns the gradient of the
-    owned planes [q_lo, q_hi)."""
+    """Inverse of ``exchange_halo`` for gradients: ``grad_buf`` covers planes [kv_lo, kv_hi); partial sums for
+    planes owned elsewhere are sent to their owners straight from the buffer, and the owner adds what it receives
+    into its planes in place.  Returns the gradient of the owned planes [q_lo, q_hi) (a view of ``grad_buf``)."""
     me = plans[rank]
-    own = grad_buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo).clone()
-    ops, recvs, keep = [], [], []
+    own = grad_buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo)
+    ops, recvs = [], []
     for other in plans:
         if other.rank == rank:
             continue
         lo, hi = _overlap(other.q_lo, other.q_hi, me.kv_lo, me.kv_hi)       # partials I hold for `other`
         if hi > lo:
-            piece = grad_buf.narrow(axis, lo - me.kv_lo, hi - lo).contiguous()
-            keep.append(piece)
-            ops.append(dist.P2POp(dist.isend, piece, _global_rank(other.rank, group), group))
+            for piece in _planes(grad_buf, axis, lo - me.kv_lo, hi - lo):
+                ops.append(dist.P2POp(dist.isend, piece, _global_rank(other.rank, group), group))
         lo, hi = _overlap(me.q_lo, me.q_hi, other.kv_lo, other.kv_hi)       # partials `other` holds for me
         if hi > lo:
             shape = list(own.shape)
             shape[axis] = hi - lo
             piece = own.new_empty(shape)
             recvs.append((piece, lo, hi))
-            ops.append(dist.P2POp(dist.irecv, piece, _global_rank(other.rank, group), group))
+            for part in _planes(piece, axis, 0, hi - lo):
+                ops.append(dist.P2POp(dist.irecv, part, _global_rank(other.rank, group), group))
     if ops:
         for req in dist.batch_isend_irecv(ops):
             req.wait()
