@@ -556,7 +556,7 @@ def run_table_workload(args):
         tens = 8 * L * 4 * 12 * 4
         logit = 8 * L * 4 * 5 * 4
         byts = (2 * tens + logit) + 2 * logit + (logit + 2 * tens)       # QK ; softmax ; AV
-        kernel_bytes = {"row_dot": 2 * tens + logit, "row_wsum": logit + 2 * tens}
+        kernel_bytes = {"row_dot": 2 * tens + logit, "row_wsum": logit + 2 * tens, "row_fused": 4 * tens}
         flops = 2 * 4.0 * 8 * 4 * L * 5 * 12 / 2                         # 2*N*K*D for QK and again for AV
 
         def eager():
@@ -573,6 +573,15 @@ def run_table_workload(args):
         step = graph.replay
         extra_cfg = {"launch": "CUDA graph replay of the three launches"}
         dtype = "f32"
+        # the same result from the one-launch fused operator (no logits in memory), for the record
+        from natten_mlx_b200.extras.allin1 import na1d_qkv_fused
+        fused_fn = lambda: na1d_qkv_fused(q, k, v, rpb, 5, 2, scale=0.288)
+        for _ in range(3):
+            fused_fn()
+        torch.cuda.synchronize()
+        fgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(fgraph):
+            fused_out = fused_fn()
     else:
         # B=16 padded to 128x128, per-sample H,W from {64,...,128}, 16 query / 4 KV heads, D=128, K=13, dilation 2,
         # 64 extra tokens, LSE returned and merged; forward + backward
@@ -617,6 +626,15 @@ def run_table_workload(args):
         for a, b in evs:
             flush.zero_()
             a.record()
+            fgraph.replay()
+            b.record()
+        torch.cuda.synchronize()
+        extra_cfg["fused_one_launch"] = {"ms_per_step": sum(a.elapsed_time(b) for a, b in evs) / args.steps,
+                                         "algorithmic_bytes": 4 * tens,
+                                         "max_abs_diff_to_split": float((fused_out - graph_out).abs().max())}
+        for a, b in evs:
+            flush.zero_()
+            a.record()
             eager()
             b.record()
         torch.cuda.synchronize()
@@ -629,7 +647,7 @@ def run_table_workload(args):
     except OSError:
         pass
     # per-kernel device time of the library's launches (eager launches bracketed by events)
-    run_eager = eager if eager is not None else step
+    run_eager = (lambda: (eager(), fused_fn())) if eager is not None else step
     _lib.trace_report()
     _lib.trace_enable(True)
     for _ in range(args.steps):

@@ -170,6 +170,16 @@ int natten_b200_qk_backward(const natten_b200_geom* g, const void* q, const void
                             const void* dlogits, void* dq, void* dk, float* dbias, void* stream);
 
 /*
+ * out[B, out..., Hq, D] = softmax_slots(scale * q . k[neighbour] + bias) . v[neighbour], optionally with the
+ * log-sum-exp lse[B, out..., Hq] (nullable): QK + relative position bias, softmax and AV in one launch, forward
+ * only, one thread per (query, head) row, the logits never reach memory.  bias as in natten_b200_qk_forward
+ * (nullable).  head_dim 8, 16, 24, 32, or 12 in float32 (NATTEN_B200_EINVAL otherwise).  The fused path of the
+ * reference's DiNAT-style ops: natten2d_qkv_fused, src/natten_mlx/extras/allin1/functional_metal.py:2130-2170.
+ */
+int natten_b200_qk_bias_av_forward(const natten_b200_geom* g, const void* q, const void* k, const void* v,
+                                   const float* bias, void* out, float* lse, void* stream);
+
+/*
  * Split AV: out = sum over valid slots of attn * v_neighbour.
  * Replaces na{1,2,3}d_av_forward (src/natten_mlx/_core/ops.py:75-82;
  * src/natten_mlx/_core/pure.py:286-317, 362-401, 452-494) and the allin1

@@ -284,6 +284,23 @@ int natten_b200_qk_backward(const natten_b200_geom* gi, const void* q, const voi
   return run_split(SplitOp::QkBackward, g, gi->dtype, q, k, dlogits, nullptr, dq, dk, dbias, (cudaStream_t)stream);
 }
 
+int natten_b200_qk_bias_av_forward(const natten_b200_geom* gi, const void* q, const void* k, const void* v,
+                                   const float* bias, void* out, float* lse, void* stream) {
+  Geo g;
+  if (int rc = make_geo(gi, &g)) return rc;
+  if (int rc = reject_pitched(g, "qk_bias_av_forward")) return rc;
+  if (any_null({q, k, v, out})) return set_error(NATTEN_B200_EINVAL, "qk_bias_av_forward: null tensor");
+  if (any_misaligned({q, k, v, out})) return reject_misaligned("qk_bias_av_forward");
+  if (bias != nullptr) {
+    for (int a = 0; a < 3; ++a)
+      if (g.st[a] != 1 || g.ca[a]) return set_error(NATTEN_B200_EINVAL, "bias requires stride 1 and no causal axis");
+  }
+  if (!run_fused_rows(g, gi->dtype, q, k, v, bias, out, lse, (cudaStream_t)stream))
+    return set_error(NATTEN_B200_EINVAL, "qk_bias_av_forward: head_dim %d is not served by the row kernels (8, 12 (float32), 16, 24, 32)",
+                     g.D);
+  return check_launch("qk_bias_av_forward");
+}
+
 int natten_b200_av_forward(const natten_b200_geom* gi, const void* attn, const void* v, void* out,
                            void* stream) {
   Geo g;

@@ -38,6 +38,8 @@ int run_split(SplitOp op, const Geo& g, int dtype, const void* a, const void* b,
 bool run_split_rows(SplitOp op, const Geo& g, int dtype, const void* a, const void* b, const void* c,
                     const float* bias, void* o0, void* o1, cudaStream_t s);
 bool run_bias_grad_rows(const Geo& g, int dtype, const void* dlogits, float* dbias, cudaStream_t s);
+bool run_fused_rows(const Geo& g, int dtype, const void* q, const void* k, const void* v, const float* bias, void* out,
+                    float* lse, cudaStream_t s);
 
 struct FusedArgs {
   const void *q, *k, *v, *k_extra, *v_extra;

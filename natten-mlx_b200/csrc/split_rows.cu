@@ -72,57 +72,108 @@ __device__ __forceinline__ long long q_row_of(const Geo& g, const Row32& r) {
   return ((long long)r.b * g.n_q + ql) * g.Hq + r.h;
 }
 
+// Walks the kernel slots of one row in row-major order (slot = (s0 * K1 + s1) * K2 + s2) and hands out, slot by
+// slot, whether the slot is valid and the row of the key it addresses.
+struct SlotWalk {
+  int s0, s1, s2, slot;
+  __device__ __forceinline__ SlotWalk() : s0(0), s1(0), s2(0), slot(0) {}
+  __device__ __forceinline__ bool next(const Geo& g, const RowWin& w, long long ybase, long long& key_row) {
+    const int x0 = w.start[0] + s0 * g.dl[0], x1 = w.start[1] + s1 * g.dl[1], x2 = w.start[2] + s2 * g.dl[2];
+    const bool ok = x0 >= 0 && x0 < w.hi[0] && x1 >= 0 && x1 < w.hi[1] && x2 >= 0 && x2 < w.hi[2];
+    key_row = ybase + ((long long)(x0 - g.ko[0]) * g.ke[1] + (x1 - g.ko[1])) * g.ke[2] + (x2 - g.ko[2]);
+    ++slot;
+    if (++s2 == g.K[2]) {
+      s2 = 0;
+      if (++s1 == g.K[1]) { s1 = 0; ++s0; }
+    }
+    return ok;
+  }
+};
+
+// Slots whose key rows are requested together, so that several loads are in flight per thread.
+template <int D> struct SlotBatch { static constexpr int n = D <= 16 ? 4 : 2; };
+
 // ---------------------------------------------------------------------------
 // row_dot: dst[row, slot] = alpha * <x[row], y[key(row, slot)]> (+ bias)
 // ---------------------------------------------------------------------------
+// The K_vol values of a row are contiguous in dst, and the rows of a warp are consecutive: a warp first collects
+// its 32 x K_vol values in shared memory (when they fit) and then writes them out as one dense run.
 template <typename T, int D>
 __global__ void __launch_bounds__(256)
 k_row_dot(Geo g, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ bias,
-          T* __restrict__ dst, float alpha, float masked_value, int x_out_indexed, int n_rows) {
-  for (long long row64 = (long long)blockIdx.x * blockDim.x + threadIdx.x; row64 < n_rows; row64 += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)row64;
-    const Row32 r = decode_row32(g, row);
+          T* __restrict__ dst, float alpha, float masked_value, int x_out_indexed, int n_rows, int staged) {
+  extern __shared__ float stage_all[];
+  constexpr int NB = SlotBatch<D>::n;
+  const int lane = threadIdx.x & 31;
+  float* stage = stage_all + (size_t)(threadIdx.x >> 5) * 32 * g.kvol;
+  const int w1 = 2 * g.K[1] - 1, w2 = 2 * g.K[2] - 1;
+  for (long long base = ((long long)blockIdx.x * blockDim.x + threadIdx.x) - lane; base < n_rows;
+       base += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)base + lane;
+    const bool live = row < n_rows;
+    const Row32 r = decode_row32(g, live ? row : 0);
     const RowWin w = row_win(g, r);
+    float* mine = stage + lane * g.kvol;
     T* drow = dst + (long long)row * g.kvol;
-    if (!w.inside) {   // padded query of a variable-size batch
-      for (int s = 0; s < g.kvol; ++s) drow[s] = from_f<T>(0.f);
-      continue;
-    }
-    float xr[D];
-    load_row<T, D>(x + (x_out_indexed ? (long long)row : q_row_of(g, r)) * D, xr);
-    const long long ybase = (long long)r.b * g.n_kv;
-    const int hk = r.h / g.rep;
-    int pb[3] = {0, 0, 0};
-    long long bias_h = 0;
-    const int w1 = 2 * g.K[1] - 1, w2 = 2 * g.K[2] - 1;
-    if (bias != nullptr) {
+    auto put = [&](int slot, float val) {
+      if (staged) mine[slot] = val;
+      else if (live) drow[slot] = from_f<T>(val);
+    };
+    if (!w.inside || !live) {          // padded query of a variable-size batch (or past the last row)
+      for (int s = 0; s < g.kvol; ++s) put(s, 0.f);
+    } else {
+      float xr[D];
+      load_row<T, D>(x + (x_out_indexed ? (long long)row : q_row_of(g, r)) * D, xr);
+      const long long ybase = (long long)r.b * g.n_kv;
+      const int hk = r.h / g.rep;
+      int pb[3] = {0, 0, 0};
+      long long bias_h = 0;
+      if (bias != nullptr) {
 #pragma unroll
-      for (int a = 0; a < 3; ++a) pb[a] = pb_start(w.p[a], w.ext[a], g.K[a], g.dl[a]);
-      bias_h = (long long)r.h * (2 * g.K[0] - 1) * w1 * w2;
-    }
-    int slot = 0;
-    for (int s0 = 0; s0 < g.K[0]; ++s0) {
-      const int x0 = w.start[0] + s0 * g.dl[0];
-      const bool v0 = x0 >= 0 && x0 < w.hi[0];
-      for (int s1 = 0; s1 < g.K[1]; ++s1) {
-        const int x1 = w.start[1] + s1 * g.dl[1];
-        const bool v1 = v0 && x1 >= 0 && x1 < w.hi[1];
-        const long long k01 = ((long long)(x0 - g.ko[0]) * g.ke[1] + (x1 - g.ko[1])) * g.ke[2] - g.ko[2];
-        for (int s2 = 0; s2 < g.K[2]; ++s2, ++slot) {
-          const int x2 = w.start[2] + s2 * g.dl[2];
-          float val = masked_value;
-          if (v1 && x2 >= 0 && x2 < w.hi[2]) {
-            float yr[D];
-            load_row<T, D>(y + ((ybase + k01 + x2) * g.Hkv + hk) * D, yr);
-            float acc = 0.f;
+        for (int a = 0; a < 3; ++a) pb[a] = pb_start(w.p[a], w.ext[a], g.K[a], g.dl[a]);
+        bias_h = (long long)r.h * (2 * g.K[0] - 1) * w1 * w2;
+      }
+      SlotWalk walk;
+      for (int s = 0; s < g.kvol; s += NB) {
+        float yr[NB][D];
+        bool ok[NB];
+        float bv[NB];
 #pragma unroll
-            for (int i = 0; i < D; ++i) acc = fmaf(xr[i], yr[i], acc);
-            val = alpha * acc;
-            if (bias != nullptr) val += bias[bias_h + ((long long)(pb[0] + s0) * w1 + (pb[1] + s1)) * w2 + (pb[2] + s2)];
+        for (int u = 0; u < NB; ++u) {
+          ok[u] = false;
+          bv[u] = 0.f;
+          if (s + u < g.kvol) {
+            const int b0 = pb[0] + walk.s0, b1 = pb[1] + walk.s1, b2 = pb[2] + walk.s2;
+            long long key_row;
+            ok[u] = walk.next(g, w, ybase, key_row);
+            if (ok[u]) {
+              load_row<T, D>(y + (key_row * g.Hkv + hk) * D, yr[u]);
+              if (bias != nullptr) bv[u] = bias[bias_h + ((long long)b0 * w1 + b1) * w2 + b2];
+            }
           }
-          drow[slot] = from_f<T>(val);
+        }
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          if (s + u < g.kvol) {
+            float val = masked_value;
+            if (ok[u]) {
+              float acc = 0.f;
+#pragma unroll
+              for (int i = 0; i < D; ++i) acc = fmaf(xr[i], yr[u][i], acc);
+              val = alpha * acc + bv[u];
+            }
+            put(s + u, val);
+          }
         }
       }
+    }
+    if (staged) {
+      __syncwarp();
+      const long long first = base * g.kvol;                       // the warp's run in dst
+      const long long total = (long long)n_rows * g.kvol;
+      for (int i = lane; i < 32 * g.kvol; i += 32)
+        if (first + i < total) dst[first + i] = from_f<T>(stage[i]);
+      __syncwarp();
     }
   }
 }
@@ -134,6 +185,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(256)
 k_row_wsum(Geo g, const T* __restrict__ wt, const T* __restrict__ y, T* __restrict__ dst, float alpha,
            int dst_q_indexed, int n_rows) {
+  constexpr int NB = SlotBatch<D>::n;
   for (long long row64 = (long long)blockIdx.x * blockDim.x + threadIdx.x; row64 < n_rows; row64 += (long long)gridDim.x * blockDim.x) {
     const int row = (int)row64;
     const Row32 r = decode_row32(g, row);
@@ -145,29 +197,113 @@ k_row_wsum(Geo g, const T* __restrict__ wt, const T* __restrict__ y, T* __restri
       const T* wrow = wt + (long long)row * g.kvol;
       const long long ybase = (long long)r.b * g.n_kv;
       const int hk = r.h / g.rep;
-      int slot = 0;
-      for (int s0 = 0; s0 < g.K[0]; ++s0) {
-        const int x0 = w.start[0] + s0 * g.dl[0];
-        const bool v0 = x0 >= 0 && x0 < w.hi[0];
-        for (int s1 = 0; s1 < g.K[1]; ++s1) {
-          const int x1 = w.start[1] + s1 * g.dl[1];
-          const bool v1 = v0 && x1 >= 0 && x1 < w.hi[1];
-          const long long k01 = ((long long)(x0 - g.ko[0]) * g.ke[1] + (x1 - g.ko[1])) * g.ke[2] - g.ko[2];
-          for (int s2 = 0; s2 < g.K[2]; ++s2, ++slot) {
-            const int x2 = w.start[2] + s2 * g.dl[2];
-            if (!(v1 && x2 >= 0 && x2 < w.hi[2])) continue;
-            const float ws = to_f<T>(wrow[slot]);
-            float yr[D];
-            load_row<T, D>(y + ((ybase + k01 + x2) * g.Hkv + hk) * D, yr);
+      SlotWalk walk;
+      for (int s = 0; s < g.kvol; s += NB) {
+        float yr[NB][D];
+        float ws[NB];
 #pragma unroll
-            for (int i = 0; i < D; ++i) acc[i] = fmaf(ws, yr[i], acc[i]);
+        for (int u = 0; u < NB; ++u) {
+          ws[u] = 0.f;
+          if (s + u < g.kvol) {
+            long long key_row;
+            if (walk.next(g, w, ybase, key_row)) {
+              ws[u] = to_f<T>(wrow[s + u]);
+              load_row<T, D>(y + (key_row * g.Hkv + hk) * D, yr[u]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < D; ++i) yr[u][i] = 0.f;
+            }
           }
         }
+#pragma unroll
+        for (int u = 0; u < NB; ++u)
+          if (s + u < g.kvol) {
+#pragma unroll
+            for (int i = 0; i < D; ++i) acc[i] = fmaf(ws[u], yr[u][i], acc[i]);
+          }
       }
     }
 #pragma unroll
     for (int i = 0; i < D; ++i) acc[i] *= alpha;
     store_row<T, D>(dst + (dst_q_indexed ? q_row_of(g, r) : (long long)row) * D, acc);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// row_fused: out[row] = softmax_slot(alpha * <q[row], k[key]> + bias) . v[key]   (forward only)
+// ---------------------------------------------------------------------------
+// QK + relative position bias, softmax and AV of one (query, head) row in one thread: the logits never reach
+// memory.  The softmax runs online over the slots (running maximum m, sum l, output acc), so any kernel volume
+// works with the same registers.  The fused path of the reference's DiNAT-style ops
+// (src/natten_mlx/extras/allin1/functional_metal.py:2130-2170).
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+k_row_fused(Geo g, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+            const float* __restrict__ bias, T* __restrict__ out, float* __restrict__ lse, int n_rows) {
+  constexpr int NB = D <= 16 ? 2 : 1;
+  const int w1 = 2 * g.K[1] - 1, w2 = 2 * g.K[2] - 1;
+  for (long long row64 = (long long)blockIdx.x * blockDim.x + threadIdx.x; row64 < n_rows; row64 += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)row64;
+    const Row32 r = decode_row32(g, row);
+    const RowWin w = row_win(g, r);
+    float acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    if (w.inside) {
+      float qr[D];
+      load_row<T, D>(q + q_row_of(g, r) * D, qr);
+      const long long ybase = (long long)r.b * g.n_kv;
+      const int hk = r.h / g.rep;
+      int pb[3] = {0, 0, 0};
+      long long bias_h = 0;
+      if (bias != nullptr) {
+#pragma unroll
+        for (int a = 0; a < 3; ++a) pb[a] = pb_start(w.p[a], w.ext[a], g.K[a], g.dl[a]);
+        bias_h = (long long)r.h * (2 * g.K[0] - 1) * w1 * w2;
+      }
+      SlotWalk walk;
+      for (int s = 0; s < g.kvol; s += NB) {
+        float kr[NB][D], vr[NB][D], bv[NB];
+        bool ok[NB];
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          ok[u] = false;
+          bv[u] = 0.f;
+          if (s + u < g.kvol) {
+            const int b0 = pb[0] + walk.s0, b1 = pb[1] + walk.s1, b2 = pb[2] + walk.s2;
+            long long key_row;
+            ok[u] = walk.next(g, w, ybase, key_row);
+            if (ok[u]) {
+              load_row<T, D>(k + (key_row * g.Hkv + hk) * D, kr[u]);
+              load_row<T, D>(v + (key_row * g.Hkv + hk) * D, vr[u]);
+              if (bias != nullptr) bv[u] = bias[bias_h + ((long long)b0 * w1 + b1) * w2 + b2];
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < NB; ++u) {
+          if (ok[u]) {
+            float d = 0.f;
+#pragma unroll
+            for (int i = 0; i < D; ++i) d = fmaf(qr[i], kr[u][i], d);
+            const float sc = g.scale * d + bv[u];
+            const float m_new = fmaxf(m, sc);
+            const float c = __expf(m - m_new);            // 0 on the first valid slot (m = -inf)
+            const float pr = __expf(sc - m_new);
+            l = l * c + pr;
+#pragma unroll
+            for (int i = 0; i < D; ++i) acc[i] = fmaf(acc[i], c, pr * vr[u][i]);
+            m = m_new;
+          }
+        }
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] *= inv;
+    store_row<T, D>(out + (long long)row * D, acc);
+    if (lse != nullptr) lse[row] = l > 0.f ? m + __logf(l) : (w.inside ? -INFINITY : 0.f);
   }
 }
 
@@ -305,9 +441,12 @@ void launch_rows(SplitOp op, const Geo& g, const T* A, const T* Bp, const T* C, 
   const int n_out_rows = (int)((long long)g.B * g.n_out * g.Hq);
   const int n_kv_rows = (int)((long long)g.B * g.n_kv * g.Hkv);
   const float ninf = -__builtin_huge_valf();
+  // the logits of a block's 256 rows pass through shared memory when they fit into the default 48 KB
+  const int staged = (size_t)256 * g.kvol * sizeof(float) <= 48 * 1024 ? 1 : 0;
+  const size_t stage_bytes = staged ? (size_t)256 * g.kvol * sizeof(float) : 0;
   switch (op) {
     case SplitOp::QkForward:
-      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, 0, s>>>(g, A, Bp, bias, o0, g.scale, ninf, 0, n_out_rows));
+      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, stage_bytes, s>>>(g, A, Bp, bias, o0, g.scale, ninf, 0, n_out_rows, staged));
       break;
     case SplitOp::QkBackward: {   // A = q, Bp = k, C = dlogits -> o0 = dq, o1 = dk
       const bool strided = g.st[0] * g.st[1] * g.st[2] != 1 || g.n_out != g.n_q;
@@ -320,7 +459,7 @@ void launch_rows(SplitOp op, const Geo& g, const T* A, const T* Bp, const T* C, 
       NB_LAUNCH("row_wsum", s, k_row_wsum<T, D><<<grid_rows(n_out_rows), 256, 0, s>>>(g, A, Bp, o0, 1.f, 0, n_out_rows));
       break;
     case SplitOp::AvBackward:     // A = attn, Bp = v, C = dout -> o0 = dattn, o1 = dv
-      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, 0, s>>>(g, C, Bp, nullptr, o0, 1.f, 0.f, 1, n_out_rows));
+      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, stage_bytes, s>>>(g, C, Bp, nullptr, o0, 1.f, 0.f, 1, n_out_rows, staged));
       NB_LAUNCH("row_inverse", s, k_row_inverse<T, D><<<grid_rows(n_kv_rows), 256, 0, s>>>(g, A, C, o1, 1.f, 1, n_kv_rows));
       break;
   }
@@ -349,7 +488,40 @@ bool dispatch_rows(SplitOp op, const Geo& g, const void* a, const void* b, const
   return false;
 }
 
+template <typename T>
+bool dispatch_fused(const Geo& g, const void* q, const void* k, const void* v, const float* bias, void* out, float* lse,
+                    cudaStream_t s) {
+  const int n_rows = (int)((long long)g.B * g.n_out * g.Hq);
+#define NB_ROW_FUSED(DD)                                                                                              \
+  NB_LAUNCH("row_fused", s, k_row_fused<T, DD><<<grid_rows(n_rows), 256, 0, s>>>(                                      \
+      g, static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), bias, static_cast<T*>(out), lse, n_rows)); \
+  return true
+  switch (g.D) {
+    case 8: NB_ROW_FUSED(8);
+    case 12:
+      if constexpr (sizeof(T) == 4) { NB_ROW_FUSED(12); }
+      return false;
+    case 16: NB_ROW_FUSED(16);
+    case 24: NB_ROW_FUSED(24);
+    case 32: NB_ROW_FUSED(32);
+  }
+#undef NB_ROW_FUSED
+  return false;
+}
+
 }  // namespace
+
+// QK + bias -> softmax -> AV of every (query, head) row in one launch (forward only); false when the head dim is
+// not one the row kernels are built for.
+bool run_fused_rows(const Geo& g, int dtype, const void* q, const void* k, const void* v, const float* bias, void* out,
+                    float* lse, cudaStream_t s) {
+  switch (dtype) {
+    case NATTEN_B200_F32: return dispatch_fused<float>(g, q, k, v, bias, out, lse, s);
+    case NATTEN_B200_F16: return dispatch_fused<__half>(g, q, k, v, bias, out, lse, s);
+    case NATTEN_B200_BF16: return dispatch_fused<__nv_bfloat16>(g, q, k, v, bias, out, lse, s);
+  }
+  return false;
+}
 
 // Serves a split operator with the row-per-thread kernels when the head dim is one of the small
 // sizes they are built for (rows are then multiples of 16 bytes); returns false otherwise.

@@ -146,6 +146,22 @@ def qk_backward(q, k, grad_attn, ks, st, dl, ca, scale, want_dbias_shape=None, s
     return (dq, dk) if dbias is None else (dq, dk, dbias)
 
 
+def qk_bias_av_forward(q, k, v, ks, dl, scale, bias=None, return_lse=False):
+    """QK + bias -> softmax -> AV in one launch (forward only, stride 1, no causal axis)."""
+    rank = q.dim() - 3
+    q, k, v = _prep(q, k, v)
+    one, no = (1,) * rank, (False,) * rank
+    g = _geom(q, k, rank, ks, one, dl, no, _scale(scale, q.shape[-1]))
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device) if return_lse else None
+    if bias is not None:
+        bias = bias.to(device=q.device, dtype=torch.float32).contiguous()
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().natten_b200_qk_bias_av_forward(g, _ptr(q), _ptr(k), _ptr(v), _ptr(bias), _ptr(out),
+                                                              _ptr(lse), _stream(q)))
+    return (out, lse) if return_lse else out
+
+
 def _check_attn(attn, v, rank, ks, st):
     kvol = 1
     for x in ks:

@@ -66,6 +66,7 @@ SYMBOLS = {
     "natten_b200_qk_forward": (ctypes.c_int, [_G, _P, _P, _P, _P, _P]),
     "natten_b200_qk_backward": (ctypes.c_int, [_G, _P, _P, _P, _P, _P, _P, _P]),
     "natten_b200_av_forward": (ctypes.c_int, [_G, _P, _P, _P, _P]),
+    "natten_b200_qk_bias_av_forward": (ctypes.c_int, [_G, _P, _P, _P, _P, _P, _P, _P]),
     "natten_b200_av_backward": (ctypes.c_int, [_G, _P, _P, _P, _P, _P, _P]),
     "natten_b200_fused_forward": (ctypes.c_int, [_G] + [_P] * 8),
     "natten_b200_fused_backward_scratch_bytes": (ctypes.c_size_t, [_G]),

@@ -64,4 +64,37 @@ def na2d_av_fused(attn, value, kernel_size: int, dilation: int = 1):
     return _ag.na2d_av_with_grad(attn, value, (k, k), (1, 1), (d, d), (False, False))
 
 
-__all__ = ["na1d_qk_rpb", "na1d_av_fused", "na2d_qk_rpb", "na2d_av_fused"]
+def _qkv_fused(rank, query, key, value, rpb, kernel_size, dilation, scale):
+    from .._core import cuda as _backend
+    k, d = int(kernel_size), int(dilation)
+    if query.dim() != rank + 3 or key.shape != query.shape[:-2] + key.shape[-2:] or value.shape != key.shape:
+        raise ValueError(f"query/key/value must be {rank + 3}D heads-last tensors of matching shape")
+    if rpb is not None:
+        want = (query.shape[-2],) + (2 * k - 1,) * rank
+        if tuple(rpb.shape) != want:
+            raise ValueError(f"rpb must have shape {want}, got {tuple(rpb.shape)}")
+    for a in range(rank):
+        if k * d > query.shape[1 + a]:
+            raise ValueError(
+                f"kernel_size * dilation must be <= axis length; got kernel_size={k}, dilation={d}, "
+                f"axis length={query.shape[1 + a]}")
+    with torch.no_grad():
+        return _backend.qk_bias_av_forward(query, key, value, (k,) * rank, (d,) * rank,
+                                           1.0 if scale is None else float(scale), bias=rpb)
+
+
+def na1d_qkv_fused(query, key, value, rpb: Optional[torch.Tensor], kernel_size: int, dilation: int = 1, *,
+                   scale: Optional[float] = None):
+    """QK + RPB -> softmax -> AV of 1D neighborhood attention in one launch (inference: no gradients).
+    Equals ``na1d_av_fused(softmax(na1d_qk_rpb(q, k, rpb)), v)`` without the logits ever reaching memory
+    (natten2d_qkv_fused of the reference, src/natten_mlx/extras/allin1/functional_metal.py:2130-2170)."""
+    return _qkv_fused(1, query, key, value, rpb, kernel_size, dilation, scale)
+
+
+def na2d_qkv_fused(query, key, value, rpb: Optional[torch.Tensor], kernel_size: int, dilation: int = 1, *,
+                   scale: Optional[float] = None):
+    """QK + RPB -> softmax -> AV of 2D neighborhood attention in one launch (inference: no gradients)."""
+    return _qkv_fused(2, query, key, value, rpb, kernel_size, dilation, scale)
+
+
+__all__ = ["na1d_qk_rpb", "na1d_av_fused", "na2d_qk_rpb", "na2d_av_fused", "na1d_qkv_fused", "na2d_qkv_fused"]

@@ -245,6 +245,35 @@ def test_config_allin1_split_1d_fp32():
     close32(out, want_o, "out")
 
 
+def test_allin1_fused_forward_matches_split_and_oracle():
+    """QK + RPB -> softmax -> AV in one launch equals the split composition and the oracle (float32 1e-4; bf16 2e-2)."""
+    shape = (8, 4096, 4, 12)
+    q, k, v = _rand(shape, 21), _rand(shape, 22), _rand(shape, 23)
+    rpb = _rand((4, 9), 24) * 0.02
+    want = oracle.av_fused(torch.softmax(oracle.qk_rpb(q, k, rpb, 5, 2, 0.288), -1), v, 5, 2)
+    before = _lib.launch_count()
+    got = allin1.na1d_qkv_fused(q.to(DEV), k.to(DEV), v.to(DEV), rpb.to(DEV), 5, 2, scale=0.288)
+    assert _lib.launch_count() - before == 1
+    close32(got, want, "fused 1d")
+    # 2D, no bias, and with bias
+    shape = (2, 9, 12, 2, 12)
+    q, k, v = _rand(shape, 41), _rand(shape, 42), _rand(shape, 43)
+    rpb = _rand((2, 5, 5), 44) * 0.02
+    for r in (None, rpb):
+        want = oracle.av_fused(torch.softmax(oracle.qk_rpb(q, k, r, 3, 2, 0.288), -1), v, 3, 2)
+        got = allin1.na2d_qkv_fused(q.to(DEV), k.to(DEV), v.to(DEV), None if r is None else r.to(DEV), 3, 2, scale=0.288)
+        close32(got, want, "fused 2d")
+    # bf16, head dim 32
+    shape = (1, 14, 10, 2, 32)
+    q, k, v = (_rand(shape, 50 + i, torch.bfloat16) for i in range(3))
+    want = oracle.av_fused(torch.softmax(oracle.qk_rpb(q.float(), k.float(), None, 5, 1, 32 ** -0.5), -1), v.float(), 5, 1)
+    got = allin1.na2d_qkv_fused(q.to(DEV), k.to(DEV), v.to(DEV), None, 5, 1, scale=32 ** -0.5)
+    close_lowp(got, want, "fused 2d bf16")
+    with pytest.raises(ValueError, match="head_dim"):
+        allin1.na1d_qkv_fused(torch.randn(1, 16, 2, 20, device=DEV), torch.randn(1, 16, 2, 20, device=DEV),
+                              torch.randn(1, 16, 2, 20, device=DEV), None, 3)
+
+
 def test_allin1_gradients_match_autograd_of_oracle():
     shape = (2, 30, 2, 12)
     q, k, v = _rand(shape, 31), _rand(shape, 32), _rand(shape, 33)
