@@ -39,6 +39,10 @@ constexpr int kTileM = 128;
 constexpr int kMaxCols = 384;            // S columns per chunk
 constexpr int kMaxWords = kMaxCols / 32;
 constexpr int kThreads = 192;            // 4 softmax warps, 1 TMA warp, 1 MMA warp
+// Tensor maps of variable-size batches travel through a ring of slots in device memory that belongs to the
+// library; a call's maps (four per (sample, dilation class) pair in the backward) must fit one slot.
+constexpr int kMapSlots = 8;
+constexpr size_t kMapSlotBytes = 256 * 1024;
 
 struct alignas(64) TmaMaps {
   CUtensorMap q[kMaxClasses];
@@ -62,6 +66,10 @@ struct FwdParams {
   int rank;              // spatial rank of the tensors (tensor-map rank = rank + 2)
   int L[3], K[3], dl[3], ca[3];
   int Mr[3], Mc[3];                   // extents behind the memory strides of the row / chunk tensors (== L when dense)
+  // queries on a stride lattice: the forward and dQ kernels tile output coordinates (row stride rst, position =
+  // coordinate * rst), the dK/dV kernel walks them as chunk columns (cst); 1 everywhere without a stride.  Mq:
+  // extents of the query tensor (dQ is laid out over positions, the statistics over outputs)
+  int rst[3], cst[3], strided, Mq[3];
   int ro0, re0, co0, ce0;             // leading-axis slab: first global plane and plane count of the row / chunk tensors
   int T[3];              // query tile extents in class coordinates
   int hpt, P;            // heads per tile, positions per tile (hpt * P == 128)
@@ -245,6 +253,13 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
     const int n = slab_hi(p.ro0 + p.re0, g0, g.dl[0]) - slab_lo(p.ro0, g0, g.dl[0]);
     if (n > nloc0) nloc0 = n;
   }
+  // extents of the tile grid (rows) and of the chunk operand, in their own coordinates
+  int lrow[3], lchunk[3];
+  for (int a = 0; a < 3; ++a) {
+    lrow[a] = ceil_div(lgmax[a], p.rst[a]);
+    lchunk[a] = ceil_div(lgmax[a], p.cst[a]);
+  }
+  if (p.rst[0] != 1) nloc0 = lrow[0];
   long long best_cost = -1;
   double best_visited = 1.0;
   int want[3] = {0, 0, 0};                       // a pinned tile shape (plan_hint)
@@ -256,12 +271,13 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
       bool skip = want[2] > 0 && (t0 != want[0] || t1 != want[1] || t2 != want[2]);
       int box[3];
       for (int a = 0; a < 3; ++a) {
-        if (g.ge[a] == 1 && T[a] != 1) skip = true;          // nothing to tile on a trivial axis
+        if (lrow[a] == 1 && T[a] != 1) skip = true;          // nothing to tile on a trivial axis
         // keys a query tile addresses: T + K - 1; queries that address a key tile: more near the
         // ends of the axis (see max_query_span)
-        int need = g.ca[a] == 2 ? g.ge[a] : T[a] + g.K[a] - 1;
+        int need = g.ca[a] == 2 ? g.ge[a] : (T[a] - 1) * p.rst[a] + g.K[a];
         if (mode == 2 && g.ca[a] == 0) need = query_span(g, a, T[a]);
-        box[a] = need < lgmax[a] ? need : lgmax[a];
+        if (mode == 2 && p.cst[a] != 1) need = ceil_div(need, p.cst[a]) + 1;     // queries on the stride lattice
+        box[a] = need < lchunk[a] ? need : lchunk[a];
         if (box[a] > 256) skip = true;                        // TMA box limit
       }
       if (skip) continue;
@@ -283,7 +299,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
       if (n_pad > 256) n_pad = (n_pad + 31) & ~31;
       if (n_pad > nmax) continue;
       long long tiles = 1;
-      for (int a = 0; a < 3; ++a) tiles *= ceil_div(a == 0 ? nloc0 : lgmax[a], T[a]);
+      for (int a = 0; a < 3; ++a) tiles *= ceil_div(a == 0 ? nloc0 : lrow[a], T[a]);
       // box rows (axes 0 and 1) that no row of a tile needs are skipped by the elementwise warps:
       // among tile shapes of equal cost the one with the fewest visited rows wins
       double visited = 1.0;
@@ -296,7 +312,7 @@ long long choose_tile(const Geo& g, FwdParams& p, int nmax, int mode, const Plan
       if (best_cost < 0 || cost < best_cost || (cost == best_cost && visited < best_visited - 1e-9)) {
         best_cost = cost;
         best_visited = visited;
-        for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(a == 0 ? nloc0 : lgmax[a], T[a]); }
+        for (int a = 0; a < 3; ++a) { p.T[a] = T[a]; p.box[a] = box[a]; p.tiles[a] = ceil_div(a == 0 ? nloc0 : lrow[a], T[a]); }
         p.chunk_axis = ca; p.R = R; p.cchunks = cch; p.n_chunks = nch; p.inner = inner;
         p.n_cols = R * inner; p.n_pad = n_pad; p.rp = rp;
       }
@@ -326,7 +342,7 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
   if (!(g.scale > 0.f)) { pl.why = "scale is not positive"; return pl; }
   int ncls = 1;
   for (int a = 0; a < 3; ++a) {
-    if (g.st[a] != 1) { pl.why = "stride > 1"; return pl; }
+    if (g.st[a] != 1 && g.dl[a] != 1) { pl.why = "stride and dilation on the same axis"; return pl; }
     if ((g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a] || g.qo[a] != 0 || g.ko[a] != 0) && (a != 0 || g.rank != 3)) {
       pl.why = "slab on an axis other than the leading axis of a 3-D volume";
       return pl;
@@ -335,6 +351,14 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
     ncls *= g.dl[a];
   }
   if (ncls > kMaxClasses) { pl.why = "more than 16 dilation classes"; return pl; }
+  if (varlen && (size_t)g.B * ncls * 4 * sizeof(CUtensorMap) > kMapSlotBytes) {
+    pl.why = "more (sample, dilation class) pairs than the tensor-map ring holds";
+    return pl;
+  }
+  const bool strided = g.st[0] * g.st[1] * g.st[2] != 1;
+  if (strided && (varlen || g.n_extra != 0 || g.pitched)) { pl.why = "stride with per-sample extents, extra tokens or mem_extent"; return pl; }
+  for (int a = 0; a < 3; ++a)
+    if (strided && (g.qe[a] != g.ge[a] || g.ke[a] != g.ge[a])) { pl.why = "stride with a slab"; return pl; }
   base.B = g.B; base.Hq = g.Hq; base.Hkv = g.Hkv; base.rep = g.rep; base.D = g.D; base.rank = g.rank;
   for (int a = 0; a < 3; ++a) { base.L[a] = g.ge[a]; base.K[a] = g.K[a]; base.dl[a] = g.dl[a]; base.ca[a] = g.ca[a]; }
   {
@@ -344,7 +368,15 @@ Plan make_plan_uncached(const Geo& g, int dtype, int mode, const PlanHint& hint)
     for (int a = 0; a < 3; ++a) {
       base.Mr[a] = slab ? (rows_are_q ? g.qe[a] : g.ke[a]) : g.me[a];
       base.Mc[a] = slab ? (rows_are_q ? g.ke[a] : g.qe[a]) : g.me[a];
+      base.Mq[a] = slab ? g.qe[a] : g.me[a];      // the query tensor's own extents
+      base.rst[a] = rows_are_q ? g.st[a] : 1;
+      base.cst[a] = rows_are_q ? 1 : g.st[a];
+      if (strided) {       // the query-side index space is the output's
+        if (rows_are_q) base.Mr[a] = g.out[a];
+        else base.Mc[a] = g.out[a];
+      }
     }
+    base.strided = strided ? 1 : 0;
     base.ro0 = rows_are_q ? g.qo[0] : g.ko[0];
     base.re0 = rows_are_q ? g.qe[0] : g.ke[0];
     base.co0 = rows_are_q ? g.ko[0] : g.qo[0];
@@ -524,14 +556,22 @@ EncodeTiledFn encode_fn() {
 // dims: (heads*D, axis rank-1, ..., axis 0, B); box_sp[a] is the box extent on
 // normalised axis a (leading trivial axes of lower-rank tensors are skipped).
 // `chunk_side`: the tensor is a chunk operand (its own slab range and strides) rather than a row operand.
+// `mem_ext`, `step` and `div` describe tensors of the query side when the queries sit on a stride lattice: the
+// extents behind the memory strides (default: Mr / Mc), the element step per axis on top of the dilation (the
+// stride for the query tensor, which is laid out over positions) and the divisor of the class length (the stride:
+// one entry per lattice point).
 int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, int heads, const int box_sp[3],
-                      bool chunk_side = false) {
+                      bool chunk_side = false, const int* mem_ext = nullptr, const int* step = nullptr,
+                      const int* div = nullptr) {
   EncodeTiledFn enc = encode_fn();
   if (enc == nullptr) return set_error(NATTEN_B200_ENODEVICE, "cuTensorMapEncodeTiled is not available");
   const int lead = 3 - p.rank;
   const cuuint32_t trank = (cuuint32_t)(p.rank + 2);
-  const int* ext = chunk_side ? p.Mc : p.Mr;
+  const int* ext = mem_ext != nullptr ? mem_ext : (chunk_side ? p.Mc : p.Mr);
   const int first0 = chunk_side ? p.co0 : p.ro0, count0 = chunk_side ? p.ce0 : p.re0;
+  static const int ones[3] = {1, 1, 1};
+  if (step == nullptr) step = ones;
+  if (div == nullptr) div = ones;
   long long stride_el[3];  // elements between consecutive coordinates on each axis
   long long s = (long long)heads * p.D;
   for (int a = 2; a >= 0; --a) { stride_el[a] = s; s *= ext[a]; }
@@ -549,16 +589,16 @@ int encode_class_maps(CUtensorMap* maps, const void* base, const FwdParams& p, i
         box[0] = (cuuint32_t)p.dblk;
         int di = 1;
         for (int a = 2; a >= lead; --a, ++di) {
-          long long n = ceil_div(p.L[a] - gcls[a], p.dl[a]);
+          long long n = ceil_div(ceil_div(p.L[a] - gcls[a], p.dl[a]), div[a]);
           long long first_plane = gcls[a];              // local plane of the class's first entry
-          if (a == 0) {                                 // leading axis: only the entries inside the local planes
+          if (a == 0 && !p.strided) {                   // leading axis: only the entries inside the local planes
             const int lo = slab_lo(first0, g0, p.dl[0]), hi = slab_hi(first0 + count0, g0, p.dl[0]);
             n = hi - lo;
             first_plane = (long long)lo * p.dl[0] + g0 - first0;
             if (n <= 0) { n = 1; first_plane = 0; }     // a class without local entries: its tiles are dead
           }
           dims[di] = (cuuint64_t)n;
-          strides[di - 1] = (cuuint64_t)(stride_el[a] * p.dl[a] * 2);
+          strides[di - 1] = (cuuint64_t)(stride_el[a] * p.dl[a] * step[a] * 2);
           box[di] = (cuuint32_t)box_sp[a];
           off += first_plane * stride_el[a];
         }

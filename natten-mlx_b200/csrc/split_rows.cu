@@ -72,6 +72,105 @@ __device__ __forceinline__ long long q_row_of(const Geo& g, const Row32& r) {
   return ((long long)r.b * g.n_q + ql) * g.Hq + r.h;
 }
 
+// ---------------------------------------------------------------------------
+// row_dot: dst[row, slot] = alpha * <x[row], y[key(row, slot)]> (+ bias)
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+k_row_dot(Geo g, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ bias,
+          T* __restrict__ dst, float alpha, float masked_value, int x_out_indexed, int n_rows) {
+  for (long long row64 = (long long)blockIdx.x * blockDim.x + threadIdx.x; row64 < n_rows; row64 += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)row64;
+    const Row32 r = decode_row32(g, row);
+    const RowWin w = row_win(g, r);
+    T* drow = dst + (long long)row * g.kvol;
+    if (!w.inside) {   // padded query of a variable-size batch
+      for (int s = 0; s < g.kvol; ++s) drow[s] = from_f<T>(0.f);
+      continue;
+    }
+    float xr[D];
+    load_row<T, D>(x + (x_out_indexed ? (long long)row : q_row_of(g, r)) * D, xr);
+    const long long ybase = (long long)r.b * g.n_kv;
+    const int hk = r.h / g.rep;
+    int pb[3] = {0, 0, 0};
+    long long bias_h = 0;
+    const int w1 = 2 * g.K[1] - 1, w2 = 2 * g.K[2] - 1;
+    if (bias != nullptr) {
+#pragma unroll
+      for (int a = 0; a < 3; ++a) pb[a] = pb_start(w.p[a], w.ext[a], g.K[a], g.dl[a]);
+      bias_h = (long long)r.h * (2 * g.K[0] - 1) * w1 * w2;
+    }
+    int slot = 0;
+    for (int s0 = 0; s0 < g.K[0]; ++s0) {
+      const int x0 = w.start[0] + s0 * g.dl[0];
+      const bool v0 = x0 >= 0 && x0 < w.hi[0];
+      for (int s1 = 0; s1 < g.K[1]; ++s1) {
+        const int x1 = w.start[1] + s1 * g.dl[1];
+        const bool v1 = v0 && x1 >= 0 && x1 < w.hi[1];
+        const long long k01 = ((long long)(x0 - g.ko[0]) * g.ke[1] + (x1 - g.ko[1])) * g.ke[2] - g.ko[2];
+        for (int s2 = 0; s2 < g.K[2]; ++s2, ++slot) {
+          const int x2 = w.start[2] + s2 * g.dl[2];
+          float val = masked_value;
+          if (v1 && x2 >= 0 && x2 < w.hi[2]) {
+            float yr[D];
+            load_row<T, D>(y + ((ybase + k01 + x2) * g.Hkv + hk) * D, yr);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < D; ++i) acc = fmaf(xr[i], yr[i], acc);
+            val = alpha * acc;
+            if (bias != nullptr) val += bias[bias_h + ((long long)(pb[0] + s0) * w1 + (pb[1] + s1)) * w2 + (pb[2] + s2)];
+          }
+          drow[slot] = from_f<T>(val);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// row_wsum: dst[row] = alpha * sum_slot w[row, slot] * y[key(row, slot)]
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256)
+k_row_wsum(Geo g, const T* __restrict__ wt, const T* __restrict__ y, T* __restrict__ dst, float alpha,
+           int dst_q_indexed, int n_rows) {
+  for (long long row64 = (long long)blockIdx.x * blockDim.x + threadIdx.x; row64 < n_rows; row64 += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)row64;
+    const Row32 r = decode_row32(g, row);
+    const RowWin w = row_win(g, r);
+    float acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    if (w.inside) {
+      const T* wrow = wt + (long long)row * g.kvol;
+      const long long ybase = (long long)r.b * g.n_kv;
+      const int hk = r.h / g.rep;
+      int slot = 0;
+      for (int s0 = 0; s0 < g.K[0]; ++s0) {
+        const int x0 = w.start[0] + s0 * g.dl[0];
+        const bool v0 = x0 >= 0 && x0 < w.hi[0];
+        for (int s1 = 0; s1 < g.K[1]; ++s1) {
+          const int x1 = w.start[1] + s1 * g.dl[1];
+          const bool v1 = v0 && x1 >= 0 && x1 < w.hi[1];
+          const long long k01 = ((long long)(x0 - g.ko[0]) * g.ke[1] + (x1 - g.ko[1])) * g.ke[2] - g.ko[2];
+          for (int s2 = 0; s2 < g.K[2]; ++s2, ++slot) {
+            const int x2 = w.start[2] + s2 * g.dl[2];
+            if (!(v1 && x2 >= 0 && x2 < w.hi[2])) continue;
+            const float ws = to_f<T>(wrow[slot]);
+            float yr[D];
+            load_row<T, D>(y + ((ybase + k01 + x2) * g.Hkv + hk) * D, yr);
+#pragma unroll
+            for (int i = 0; i < D; ++i) acc[i] = fmaf(ws, yr[i], acc[i]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] *= alpha;
+    store_row<T, D>(dst + (dst_q_indexed ? q_row_of(g, r) : (long long)row) * D, acc);
+  }
+}
+
 // Walks the kernel slots of one row in row-major order (slot = (s0 * K1 + s1) * K2 + s2) and hands out, slot by
 // slot, whether the slot is valid and the row of the key it addresses.
 struct SlotWalk {
@@ -89,145 +188,6 @@ struct SlotWalk {
     return ok;
   }
 };
-
-// Slots whose key rows are requested together, so that several loads are in flight per thread.
-template <int D> struct SlotBatch { static constexpr int n = D <= 16 ? 4 : 2; };
-
-// ---------------------------------------------------------------------------
-// row_dot: dst[row, slot] = alpha * <x[row], y[key(row, slot)]> (+ bias)
-// ---------------------------------------------------------------------------
-// The K_vol values of a row are contiguous in dst, and the rows of a warp are consecutive: a warp first collects
-// its 32 x K_vol values in shared memory (when they fit) and then writes them out as one dense run.
-template <typename T, int D>
-__global__ void __launch_bounds__(256)
-k_row_dot(Geo g, const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ bias,
-          T* __restrict__ dst, float alpha, float masked_value, int x_out_indexed, int n_rows, int staged) {
-  extern __shared__ float stage_all[];
-  constexpr int NB = SlotBatch<D>::n;
-  const int lane = threadIdx.x & 31;
-  float* stage = stage_all + (size_t)(threadIdx.x >> 5) * 32 * g.kvol;
-  const int w1 = 2 * g.K[1] - 1, w2 = 2 * g.K[2] - 1;
-  for (long long base = ((long long)blockIdx.x * blockDim.x + threadIdx.x) - lane; base < n_rows;
-       base += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)base + lane;
-    const bool live = row < n_rows;
-    const Row32 r = decode_row32(g, live ? row : 0);
-    const RowWin w = row_win(g, r);
-    float* mine = stage + lane * g.kvol;
-    T* drow = dst + (long long)row * g.kvol;
-    auto put = [&](int slot, float val) {
-      if (staged) mine[slot] = val;
-      else if (live) drow[slot] = from_f<T>(val);
-    };
-    if (!w.inside || !live) {          // padded query of a variable-size batch (or past the last row)
-      for (int s = 0; s < g.kvol; ++s) put(s, 0.f);
-    } else {
-      float xr[D];
-      load_row<T, D>(x + (x_out_indexed ? (long long)row : q_row_of(g, r)) * D, xr);
-      const long long ybase = (long long)r.b * g.n_kv;
-      const int hk = r.h / g.rep;
-      int pb[3] = {0, 0, 0};
-      long long bias_h = 0;
-      if (bias != nullptr) {
-#pragma unroll
-        for (int a = 0; a < 3; ++a) pb[a] = pb_start(w.p[a], w.ext[a], g.K[a], g.dl[a]);
-        bias_h = (long long)r.h * (2 * g.K[0] - 1) * w1 * w2;
-      }
-      SlotWalk walk;
-      for (int s = 0; s < g.kvol; s += NB) {
-        float yr[NB][D];
-        bool ok[NB];
-        float bv[NB];
-#pragma unroll
-        for (int u = 0; u < NB; ++u) {
-          ok[u] = false;
-          bv[u] = 0.f;
-          if (s + u < g.kvol) {
-            const int b0 = pb[0] + walk.s0, b1 = pb[1] + walk.s1, b2 = pb[2] + walk.s2;
-            long long key_row;
-            ok[u] = walk.next(g, w, ybase, key_row);
-            if (ok[u]) {
-              load_row<T, D>(y + (key_row * g.Hkv + hk) * D, yr[u]);
-              if (bias != nullptr) bv[u] = bias[bias_h + ((long long)b0 * w1 + b1) * w2 + b2];
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < NB; ++u) {
-          if (s + u < g.kvol) {
-            float val = masked_value;
-            if (ok[u]) {
-              float acc = 0.f;
-#pragma unroll
-              for (int i = 0; i < D; ++i) acc = fmaf(xr[i], yr[u][i], acc);
-              val = alpha * acc + bv[u];
-            }
-            put(s + u, val);
-          }
-        }
-      }
-    }
-    if (staged) {
-      __syncwarp();
-      const long long first = base * g.kvol;                       // the warp's run in dst
-      const long long total = (long long)n_rows * g.kvol;
-      for (int i = lane; i < 32 * g.kvol; i += 32)
-        if (first + i < total) dst[first + i] = from_f<T>(stage[i]);
-      __syncwarp();
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
-// row_wsum: dst[row] = alpha * sum_slot w[row, slot] * y[key(row, slot)]
-// ---------------------------------------------------------------------------
-template <typename T, int D>
-__global__ void __launch_bounds__(256)
-k_row_wsum(Geo g, const T* __restrict__ wt, const T* __restrict__ y, T* __restrict__ dst, float alpha,
-           int dst_q_indexed, int n_rows) {
-  constexpr int NB = SlotBatch<D>::n;
-  for (long long row64 = (long long)blockIdx.x * blockDim.x + threadIdx.x; row64 < n_rows; row64 += (long long)gridDim.x * blockDim.x) {
-    const int row = (int)row64;
-    const Row32 r = decode_row32(g, row);
-    const RowWin w = row_win(g, r);
-    float acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
-    if (w.inside) {
-      const T* wrow = wt + (long long)row * g.kvol;
-      const long long ybase = (long long)r.b * g.n_kv;
-      const int hk = r.h / g.rep;
-      SlotWalk walk;
-      for (int s = 0; s < g.kvol; s += NB) {
-        float yr[NB][D];
-        float ws[NB];
-#pragma unroll
-        for (int u = 0; u < NB; ++u) {
-          ws[u] = 0.f;
-          if (s + u < g.kvol) {
-            long long key_row;
-            if (walk.next(g, w, ybase, key_row)) {
-              ws[u] = to_f<T>(wrow[s + u]);
-              load_row<T, D>(y + (key_row * g.Hkv + hk) * D, yr[u]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < D; ++i) yr[u][i] = 0.f;
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < NB; ++u)
-          if (s + u < g.kvol) {
-#pragma unroll
-            for (int i = 0; i < D; ++i) acc[i] = fmaf(ws[u], yr[u][i], acc[i]);
-          }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] *= alpha;
-    store_row<T, D>(dst + (dst_q_indexed ? q_row_of(g, r) : (long long)row) * D, acc);
-  }
-}
 
 // ---------------------------------------------------------------------------
 // row_fused: out[row] = softmax_slot(alpha * <q[row], k[key]> + bias) . v[key]   (forward only)
@@ -441,12 +401,9 @@ void launch_rows(SplitOp op, const Geo& g, const T* A, const T* Bp, const T* C, 
   const int n_out_rows = (int)((long long)g.B * g.n_out * g.Hq);
   const int n_kv_rows = (int)((long long)g.B * g.n_kv * g.Hkv);
   const float ninf = -__builtin_huge_valf();
-  // the logits of a block's 256 rows pass through shared memory when they fit into the default 48 KB
-  const int staged = (size_t)256 * g.kvol * sizeof(float) <= 48 * 1024 ? 1 : 0;
-  const size_t stage_bytes = staged ? (size_t)256 * g.kvol * sizeof(float) : 0;
   switch (op) {
     case SplitOp::QkForward:
-      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, stage_bytes, s>>>(g, A, Bp, bias, o0, g.scale, ninf, 0, n_out_rows, staged));
+      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, 0, s>>>(g, A, Bp, bias, o0, g.scale, ninf, 0, n_out_rows));
       break;
     case SplitOp::QkBackward: {   // A = q, Bp = k, C = dlogits -> o0 = dq, o1 = dk
       const bool strided = g.st[0] * g.st[1] * g.st[2] != 1 || g.n_out != g.n_q;
@@ -459,7 +416,7 @@ void launch_rows(SplitOp op, const Geo& g, const T* A, const T* Bp, const T* C, 
       NB_LAUNCH("row_wsum", s, k_row_wsum<T, D><<<grid_rows(n_out_rows), 256, 0, s>>>(g, A, Bp, o0, 1.f, 0, n_out_rows));
       break;
     case SplitOp::AvBackward:     // A = attn, Bp = v, C = dout -> o0 = dattn, o1 = dv
-      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, stage_bytes, s>>>(g, C, Bp, nullptr, o0, 1.f, 0.f, 1, n_out_rows, staged));
+      NB_LAUNCH("row_dot", s, k_row_dot<T, D><<<grid_rows(n_out_rows), 256, 0, s>>>(g, C, Bp, nullptr, o0, 1.f, 0.f, 1, n_out_rows));
       NB_LAUNCH("row_inverse", s, k_row_inverse<T, D><<<grid_rows(n_kv_rows), 256, 0, s>>>(g, A, C, o1, 1.f, 1, n_kv_rows));
       break;
   }

@@ -95,7 +95,7 @@ int main() {
   long long* out; cudaMalloc(&out, 64);
   cudaFuncSetAttribute(k_bench, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
   const char* names[] = {"SS QK-like", "TS PV-like", "QK+PV chunk", "SS N=256", "TS alt-acc", "bwd chunk"};
-  struct Cfg { int RB, layout, npad, D; } cfgs[] = {{64, 4, 96, 32}, {128, 2, 64, 64}, {128, 2, 128, 64}, {64, 4, 48, 32}};
+  struct Cfg { int RB, layout, npad, D; } cfgs[] = {{64, 4, 96, 32}, {128, 2, 64, 64}, {128, 2, 128, 64}, {64, 4, 48, 32}, {32, 6, 96, 32}, {32, 6, 48, 32}, {32, 0, 96, 32}};
   for (auto c : cfgs)
     for (int grid : {1, 148, 296})
       for (int pat = 0; pat < 6; ++pat) {

@@ -33,7 +33,7 @@ def _worker(rank, world, port, causal, results):
         from natten_mlx_b200 import sharding
         T, ks, dl, ca = 12, (3, 3, 5), (2, 1, 1), (causal, False, False)
         gen = torch.Generator().manual_seed(21)
-        full = [torch.randn((1, T, 6, 9, 2, 16), generator=gen) for _ in range(4)]      # q, k, v, cotangent
+        full = [torch.randn((2, T, 6, 9, 2, 16), generator=gen) for _ in range(4)]      # q, k, v, cotangent (two samples: halo planes travel per sample)
         bounds = sharding.shard_bounds(T, world)
         lo, hi = bounds[rank], bounds[rank + 1]
         dev = torch.device("cuda", rank)

@@ -1,7 +1,7 @@
 """The tensor-core (tcgen05 / TMEM / TMA) fused kernels against the CPU oracle
 and against the CUDA-core kernels, through the C ABI with the kernel family
 forced.  bf16 / fp16 tolerance against the float32 oracle: 2e-2 of the largest reference
-magnitude and 4e-2 per element (|err| <= 4e-2 * (|ref| + rms(ref)))."""
+magnitude and 5e-2 per element (|err| <= 5e-2 * (|ref| + rms(ref)))."""
 
 from __future__ import annotations
 
@@ -80,8 +80,47 @@ def test_tcgen05_is_refused_for_unsupported_shapes():
     with pytest.raises(ValueError, match="tcgen05"):
         backend.fused_forward(q, q, q, (3,), (1,), (1,), (False,), None, path="tcgen05")
     q = torch.randn(1, 16, 2, 32, device=DEV, dtype=torch.bfloat16)
-    with pytest.raises(ValueError, match="stride"):
-        backend.fused_forward(q, q, q, (3,), (2,), (1,), (False,), None, path="tcgen05")
+    with pytest.raises(ValueError, match="stride and dilation"):
+        backend.fused_forward(q, q, q, (3,), (2,), (2,), (False,), None, path="tcgen05")
+
+
+STRIDED = [
+    # shape, heads_kv, kernel, stride, dilation, causal
+    ((2, 30, 23, 2, 32), 2, (5, 7), (2, 3), (1, 1), (False, False)),
+    ((1, 24, 28, 4, 64), 2, (3, 5), (2, 1), (1, 2), (False, True)),       # a strided axis beside a dilated one; GQA
+    ((2, 150, 4, 32), 4, (7,), (2,), (1,), (False,)),
+    ((1, 57, 2, 64), 2, (9,), (4,), (1,), (True,)),
+    ((1, 6, 13, 12, 2, 32), 2, (3, 5, 3), (1, 2, 2), (1, 1, 1), (True, False, False)),
+    ((2, 56, 56, 4, 32), 4, (7, 7), (2, 2), (1, 1), (False, False)),      # several tiles per CTA
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,hkv,ks,st,dl,ca", STRIDED)
+def test_tcgen05_strided_forward_backward(dtype, shape, hkv, ks, st, dl, ca):
+    """Queries on a stride lattice on the tensor-core kernels (src/natten_mlx/_core/pure.py:19-21): out, lse and
+    all gradients against the oracle; dQ rows off the lattice are exact zeros."""
+    rank = len(shape) - 3
+    kv_shape = shape[:-2] + (hkv, shape[-1])
+    q, k, v = _rand(shape, 1, dtype), _rand(kv_shape, 2, dtype), _rand(kv_shape, 3, dtype)
+    outs = tuple(-(-shape[1 + a] // st[a]) for a in range(rank))
+    cot = _rand((shape[0],) + outs + shape[-2:], 4, dtype)
+    cot_l = _rand((shape[0],) + outs + (shape[-2],), 5, torch.float32)
+    fn = lambda a, b, c: oracle.na(a, b, c, ks, st, dl, ca, return_lse=True)
+    (o_ref, l_ref), g_ref = oracle.grads(fn, [q.float(), k.float(), v.float()], (cot.float(), cot_l))
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    out, lse = backend.fused_forward(qd, kd, vd, ks, st, dl, ca, None, path="tcgen05")
+    dq, dk, dv, _, _ = backend.fused_backward(qd, kd, vd, out, lse, cot.to(DEV), cot_l.to(DEV), ks, st, dl, ca, None,
+                                              path="tcgen05")
+    torch.cuda.synchronize()
+    assert _lib.last_path() == "tcgen05" and _lib.kernel_status() == 0
+    _check(out, o_ref, "out")
+    _check(lse, l_ref, "lse")
+    for name, got, want in zip(("dq", "dk", "dv"), (dq, dk, dv), g_ref):
+        _check(got, want, name)
+    on = torch.zeros(shape[1:1 + rank], dtype=torch.bool)
+    on[tuple(slice(0, None, s_) for s_ in st)] = True
+    assert float(dq[:, ~on.to(DEV)].abs().sum()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -141,3 +180,23 @@ def test_leading_axis_slabs_on_the_tensor_core_kernels(shape, ks, dl, ca, world)
         dv_full[:, plan.kv_lo:plan.kv_hi] += dv_.float()
     assert _rel(dk_full, g_ref[1]) < 2e-2
     assert _rel(dv_full, g_ref[2]) < 2e-2
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
+def test_two_devices_in_one_process():
+    """The opt-in to large dynamic shared memory belongs to a device's context: the tensor-core kernels must launch
+    on a second device of the same process too, and give the same bits there."""
+    shape, ks = (1, 24, 20, 4, 32), (7, 5)
+    q, k, v = (_rand(shape, 200 + i, torch.bfloat16) for i in range(3))
+    outs = []
+    for dev in ("cuda:0", "cuda:1"):
+        o, lse = backend.fused_forward(q.to(dev), k.to(dev), v.to(dev), ks, (1, 1), (1, 1), (False, False), None,
+                                       path="tcgen05")
+        g = backend.fused_backward(q.to(dev), k.to(dev), v.to(dev), o, lse, torch.ones_like(o), None, ks, (1, 1), (1, 1),
+                                   (False, False), None, path="tcgen05")
+        torch.cuda.synchronize(dev)
+        with torch.cuda.device(dev):
+            assert _lib.kernel_status() == 0
+        outs.append([t.cpu() for t in (o, lse) + tuple(g[:3])])
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
