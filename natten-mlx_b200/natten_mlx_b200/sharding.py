@@ -109,24 +109,9 @@ def _is_view_of_own_planes(local: torch.Tensor, me: SlabPlan, axis: int) -> Opti
     return base
 
 
-def exchange_halo(local: torch.Tensor, plans: Sequence[SlabPlan], rank: int, group=None, axis: int = 1) -> torch.Tensor:
-    """Return the K (or V) buffer covering planes [kv_lo, kv_hi) of this rank.
-
-    ``local`` holds the owned planes [q_lo, q_hi) along ``axis``.  Planes owned by other ranks are received
-    straight into their place in the buffer; this rank sends the planes others need straight from ``local``
-    (no staging copies: transfers go plane range by plane range, per leading index where a range is not
-    dense).  When ``local`` already is the owned-planes view of a ``halo_buffer`` nothing is copied at all.
-    All ranks must call this in the same order.
-    """
+def _halo_ops(local, buf, plans, rank, group, axis):
+    """Point-to-point operations that fill the halo planes of ``buf`` and lend this rank's planes to the others."""
     me = plans[rank]
-    if me.kv_lo == me.q_lo and me.kv_hi == me.q_hi:
-        buf = local if local.is_contiguous() else local.contiguous()       # this rank borrows nothing (it may still lend)
-        local = buf
-    else:
-        buf = _is_view_of_own_planes(local, me, axis)
-        if buf is None:
-            buf, own = halo_buffer(local, plans, rank, axis)
-            own.copy_(local)
     ops = []
     for other in plans:
         if other.rank == rank:
@@ -139,40 +124,80 @@ def exchange_halo(local: torch.Tensor, plans: Sequence[SlabPlan], rank: int, gro
         if hi > lo:
             for piece in _planes(buf, axis, lo - me.kv_lo, hi - lo):
                 ops.append(dist.P2POp(dist.irecv, piece, _global_rank(other.rank, group), group))
+    return ops
+
+
+def exchange_halos(locals_: Sequence[torch.Tensor], plans: Sequence[SlabPlan], rank: int, group=None,
+                   axis: int = 1) -> List[torch.Tensor]:
+    """Return, for every tensor of ``locals_`` (K, V, ...), the buffer covering planes [kv_lo, kv_hi) of this rank.
+
+    Each tensor holds the owned planes [q_lo, q_hi) along ``axis``.  Planes owned by other ranks are received
+    straight into their place in the buffer; this rank sends the planes others need straight from its tensor
+    (no staging copies: transfers go plane range by plane range, per leading index where a range is not
+    dense).  A tensor that already is the owned-planes view of a ``halo_buffer`` is not copied at all.  The
+    transfers of all tensors travel as one batch.  All ranks must call this in the same order.
+    """
+    me = plans[rank]
+    bufs, ops = [], []
+    for local in locals_:
+        if me.kv_lo == me.q_lo and me.kv_hi == me.q_hi:
+            buf = local if local.is_contiguous() else local.contiguous()   # this rank borrows nothing (it may still lend)
+            local = buf
+        else:
+            buf = _is_view_of_own_planes(local, me, axis)
+            if buf is None:
+                buf, own = halo_buffer(local, plans, rank, axis)
+                own.copy_(local)
+        bufs.append(buf)
+        ops += _halo_ops(local, buf, plans, rank, group, axis)
     if ops:
         for req in dist.batch_isend_irecv(ops):
             req.wait()
-    return buf
+    return bufs
+
+
+def exchange_halo(local: torch.Tensor, plans: Sequence[SlabPlan], rank: int, group=None, axis: int = 1) -> torch.Tensor:
+    """``exchange_halos`` for one tensor."""
+    return exchange_halos([local], plans, rank, group, axis)[0]
+
+
+def reduce_halo_grads_many(grad_bufs: Sequence[torch.Tensor], plans: Sequence[SlabPlan], rank: int, group=None,
+                           axis: int = 1) -> List[torch.Tensor]:
+    """Inverse of ``exchange_halos`` for gradients: every buffer covers planes [kv_lo, kv_hi); partial sums for
+    planes owned elsewhere are sent to their owners straight from the buffer, and the owner adds what it receives
+    into its planes in place.  Returns the gradients of the owned planes [q_lo, q_hi) (views of the buffers).
+    The transfers of all buffers travel as one batch."""
+    me = plans[rank]
+    owns, ops, recvs = [], [], []
+    for grad_buf in grad_bufs:
+        own = grad_buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo)
+        owns.append(own)
+        for other in plans:
+            if other.rank == rank:
+                continue
+            lo, hi = _overlap(other.q_lo, other.q_hi, me.kv_lo, me.kv_hi)       # partials I hold for `other`
+            if hi > lo:
+                for piece in _planes(grad_buf, axis, lo - me.kv_lo, hi - lo):
+                    ops.append(dist.P2POp(dist.isend, piece, _global_rank(other.rank, group), group))
+            lo, hi = _overlap(me.q_lo, me.q_hi, other.kv_lo, other.kv_hi)       # partials `other` holds for me
+            if hi > lo:
+                shape = list(own.shape)
+                shape[axis] = hi - lo
+                piece = own.new_empty(shape)
+                recvs.append((own, piece, lo, hi))
+                for part in _planes(piece, axis, 0, hi - lo):
+                    ops.append(dist.P2POp(dist.irecv, part, _global_rank(other.rank, group), group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    for own, piece, lo, hi in recvs:
+        own.narrow(axis, lo - me.q_lo, hi - lo).add_(piece)
+    return owns
 
 
 def reduce_halo_grads(grad_buf: torch.Tensor, plans: Sequence[SlabPlan], rank: int, group=None, axis: int = 1) -> torch.Tensor:
-    """Inverse of ``exchange_halo`` for gradients: ``grad_buf`` covers planes [kv_lo, kv_hi); partial sums for
-    planes owned elsewhere are sent to their owners straight from the buffer, and the owner adds what it receives
-    into its planes in place.  Returns the gradient of the owned planes [q_lo, q_hi) (a view of ``grad_buf``)."""
-    me = plans[rank]
-    own = grad_buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo)
-    ops, recvs = [], []
-    for other in plans:
-        if other.rank == rank:
-            continue
-        lo, hi = _overlap(other.q_lo, other.q_hi, me.kv_lo, me.kv_hi)       # partials I hold for `other`
-        if hi > lo:
-            for piece in _planes(grad_buf, axis, lo - me.kv_lo, hi - lo):
-                ops.append(dist.P2POp(dist.isend, piece, _global_rank(other.rank, group), group))
-        lo, hi = _overlap(me.q_lo, me.q_hi, other.kv_lo, other.kv_hi)       # partials `other` holds for me
-        if hi > lo:
-            shape = list(own.shape)
-            shape[axis] = hi - lo
-            piece = own.new_empty(shape)
-            recvs.append((piece, lo, hi))
-            for part in _planes(piece, axis, 0, hi - lo):
-                ops.append(dist.P2POp(dist.irecv, part, _global_rank(other.rank, group), group))
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-    for piece, lo, hi in recvs:
-        own.narrow(axis, lo - me.q_lo, hi - lo).add_(piece)
-    return own
+    """``reduce_halo_grads_many`` for one buffer."""
+    return reduce_halo_grads_many([grad_buf], plans, rank, group, axis)[0]
 
 
 def _global_rank(group_rank: int, group) -> int:
@@ -200,8 +225,7 @@ def fused_slab_forward_backward(q, k_buf, v_buf, grad_out, plan: SlabPlan, exten
 class _ShardedNA(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, extent, ks, dl, ca, scale, plans, rank, group):
-        k_buf = exchange_halo(k, plans, rank, group)
-        v_buf = exchange_halo(v, plans, rank, group)
+        k_buf, v_buf = exchange_halos([k, v], plans, rank, group)
         slab = _slab(plans[rank], extent)
         one = (1,) * len(extent)
         out, lse = _cuda.fused_forward(q, k_buf, v_buf, ks, one, dl, ca, scale, slab=slab)
@@ -217,8 +241,7 @@ class _ShardedNA(torch.autograd.Function):
             grad_out = torch.zeros_like(out)
         dq, dk, dv, _, _ = _cuda.fused_backward(q, k_buf, v_buf, out, lse, grad_out, grad_lse, ks, one, dl, ca,
                                                 scale, slab=slab)
-        dk = reduce_halo_grads(dk, plans, rank, group)
-        dv = reduce_halo_grads(dv, plans, rank, group)
+        dk, dv = reduce_halo_grads_many([dk, dv], plans, rank, group)
         return (dq, dk, dv) + (None,) * 8
 
 
