@@ -507,7 +507,7 @@ def run_video_legs(args, rank, world, dev, timed, barrier):
                                 "kernels_rank0": kernels, "kernel_ms_per_step_rank0": ksum}
         del r
         torch.cuda.empty_cache()
-    # (b) sharded along T: K/V halo planes by point-to-point send/recv (NCCL)
+    # (b) sharded along T: K/V halo planes written into the neighbour's buffers by the library's copy kernel
     B, T = w["shape"][0], w["shape"][1]
     if world <= T:
         bounds = sharding.shard_bounds(T, world)
@@ -515,27 +515,36 @@ def run_video_legs(args, rank, world, dev, timed, barrier):
         gen = torch.Generator().manual_seed(1240 + rank)
         local = (B, hi - lo) + tuple(w["shape"][2:])
         ks, dl, ca = w["kernel"], w["dilations"][0], w["causal"]
-        plans = sharding.all_plans(T, world, ks[0], dl[0], ca[0])
         mk = lambda: torch.randn(local, generator=gen, dtype=torch.float32).to(torch.bfloat16).to(dev)
         q, cot = mk().requires_grad_(True), mk()
-        # K and V live in buffers with room for the halo planes: the exchange receives straight into them
-        kb, k = sharding.halo_buffer(q.detach(), plans, rank)
-        vb, v = sharding.halo_buffer(q.detach(), plans, rank)
-        k.copy_(mk())
-        v.copy_(mk())
-        k.requires_grad_(True)
-        v.requires_grad_(True)
+        peer = world > 1 and sharding.peer_transport() is not None
+        if peer:
+            # K and V are produced straight into symmetric memory with room for the halo planes around them
+            plans = sharding.all_plans(T, world, ks[0], dl[0], ca[0])
+            (k, v), kv_lease = sharding.peer_kv_buffers(local, torch.bfloat16, plans, rank)
+            k.copy_(mk())
+            v.copy_(mk())
+            k.requires_grad_(True)
+            v.requires_grad_(True)
+        else:
+            k, v = mk().requires_grad_(True), mk().requires_grad_(True)
 
-        def step():
-            o = nb.na3d(q, k, v, kernel_size=ks, dilation=dl, is_causal=ca) if world == 1 else \
-                sharding.na_sharded(q, k, v, T, ks, dl, ca)
-            return torch.autograd.grad(o, (q, k, v), cot)
-        ms, kernels, ksum = traced(step)
+        def make_step(transport):
+            def step():
+                o = nb.na3d(q, k, v, kernel_size=ks, dilation=dl, is_causal=ca) if world == 1 else \
+                    sharding.na_sharded(q, k, v, T, ks, dl, ca, transport=transport)
+                return torch.autograd.grad(o, (q, k, v), cot)
+            return step
+        ms_p2p = traced(make_step("p2p"))[0] if world > 1 else None
+        ms, kernels, ksum = traced(make_step("auto"))
         out["t_sharded"] = {"ms_per_step": ms, "planes_per_rank": [bounds[r + 1] - bounds[r] for r in range(world)],
                             "value": flops_step(w) / (ms * 1e-3) / 1e12, "kernels_rank0": kernels,
-                            "kernel_ms_per_step_rank0": ksum,
-                            "halo": "K/V planes received straight into the halo planes of the K/V buffers; dK/dV partials "
-                                    "of the halo planes sent back and added in place"}
+                            "kernel_ms_per_step_rank0": ksum, "ms_per_step_nccl_send_recv": ms_p2p,
+                            "halo": "none (one rank)" if world == 1 else (
+                                "K/V planes written into the neighbour's symmetric-memory K/V buffer by the library's copy "
+                                "kernel between two flag barriers; dK/dV partials of the halo planes written into the "
+                                "owner's staging area the same way and added in place" if peer else
+                                "K/V planes and dK/dV partials by NCCL send/recv")}
     return out
 
 
@@ -706,16 +715,26 @@ def run_tshard(args, rank, world, local_rank):
     lo, hi = bounds[rank], bounds[rank + 1]
     gen = torch.Generator().manual_seed(1240 + rank)
     local = (B, hi - lo) + tuple(w["shape"][2:])
-    q, k, v, cot = (torch.randn(local, generator=gen, dtype=torch.float32).to(torch.bfloat16).to(dev) for _ in range(4))
-    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+    q, k0, v0, cot = (torch.randn(local, generator=gen, dtype=torch.float32).to(torch.bfloat16).to(dev) for _ in range(4))
     ks, dl, ca = w["kernel"], w["dilations"][0], w["causal"]
+    if world > 1 and sharding.peer_transport() is not None:
+        # K and V are produced straight into symmetric memory with room for the halo planes around them
+        (k, v), kv_lease = sharding.peer_kv_buffers(local, torch.bfloat16, sharding.all_plans(T, world, ks[0], dl[0], ca[0]), rank)
+        k.copy_(k0)
+        v.copy_(v0)
+    else:
+        k, v = k0, v0
+    del k0, v0
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
 
-    def step():
-        if world == 1:
-            out = nb.na3d(q, k, v, kernel_size=ks, dilation=dl, is_causal=ca)
-        else:
-            out = sharding.na_sharded(q, k, v, T, ks, dl, ca)
-        return torch.autograd.grad(out, (q, k, v), cot)
+    def make_step(transport):
+        def step():
+            if world == 1:
+                out = nb.na3d(q, k, v, kernel_size=ks, dilation=dl, is_causal=ca)
+            else:
+                out = sharding.na_sharded(q, k, v, T, ks, dl, ca, transport=transport)
+            return torch.autograd.grad(out, (q, k, v), cot)
+        return step
 
     def barrier():
         if world > 1:
@@ -723,32 +742,47 @@ def run_tshard(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    for _ in range(max(args.warmup, 3)):
-        step()
+
+    def timed(step, trace):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        barrier()
+        if trace:
+            _lib.trace_report()
+            _lib.trace_enable(True)               # per-kernel device times of this rank (events around each launch)
+        count0 = _lib.launch_count()
+        for a, b in evs:
+            flush.zero_()
+            if world > 1:
+                dist.barrier()                    # every rank starts a step together: the halo exchange is inside it
+            a.record()
+            step()
+            b.record()
+        barrier()
+        count = _lib.launch_count() - count0
+        kernels = None
+        if trace:
+            _lib.trace_enable(False)
+            kernels = {k: {"launches": n, "ms_per_launch": t / n} for k, (n, t) in sorted(_lib.trace_report().items())}
+        ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, kernels, count
+
+    # the same step with NCCL send/recv as the transport, for comparison (untraced, before the measured run)
+    ms_p2p = timed(make_step("p2p"), False)[0] if world > 1 else None
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    launches0 = _lib.launch_count()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    _lib.trace_report()
-    _lib.trace_enable(True)                   # per-kernel device times of this rank (events around each launch)
-    for a, b in evs:
-        flush.zero_()
-        if world > 1:
-            dist.barrier()                    # every rank starts a step together: the halo exchange is inside it
-        a.record()
-        step()
-        b.record()
-    barrier()
-    _lib.trace_enable(False)
-    kernels = {k: {"launches": n, "ms_per_launch": t / n} for k, (n, t) in sorted(_lib.trace_report().items())}
-    ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    launches = _lib.launch_count() - launches0
+    ms, kernels, launches = timed(make_step("auto"), True)
+    transport = "none (one rank)" if world == 1 else (
+        "the library's copy kernel into the neighbour's symmetric memory, flag barriers"
+        if sharding.peer_transport() is not None else "NCCL send/recv")
+    if _lib.kernel_status() != 0:
+        raise RuntimeError("a bounded wait of a kernel ran out during the timed region")
     clocks = sampler.stop() if rank == 0 else None
     if rank != 0:
         return
@@ -757,7 +791,8 @@ def run_tshard(args, rank, world, local_rank):
         "metric": "na_fwd_bwd_effective_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": w["label"] + f", sharded along T over {world} rank(s), K/V halo planes by NCCL send/recv",
+        "config": {"workload": w["label"] + f", sharded along T over {world} rank(s)", "halo_transport": transport,
+                   "ms_per_step_nccl_send_recv": ms_p2p,
                    "planes_per_rank": [bounds[r + 1] - bounds[r] for r in range(world)],
                    "l2": "256 MiB buffer written between timed iterations", "kernel_family": _lib.last_path()},
         "roofline": None, "kernels_rank0": kernels, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches),

@@ -211,9 +211,10 @@ int natten_b200_fused_forward(const natten_b200_geom* g, const void* q, const vo
                               void* out, float* lse, void* stream);
 
 /*
- * 1 when a tensor-core kernel launched by this library on the current device
- * gave up on one of its bounded waits since the last call (its results are
- * then invalid), 0 otherwise.  Synchronises with the device.  Stands where the
+ * Non-zero when a kernel launched by this library on the current device gave
+ * up on one of its bounded waits since the last call (its results are then
+ * invalid): 1 a tensor-core kernel, 2 natten_b200_peer_barrier.  0 otherwise.
+ * Synchronises with the device.  Stands where the
  * reference turns a failed accelerated kernel into a silent fallback
  * (src/natten_mlx/_core/fast_metal.py:2003-2016): here it is reported instead.
  */
@@ -276,6 +277,33 @@ int natten_b200_fused_backward_static_scratch(const natten_b200_geom* g, const v
                                               const void* out, const float* lse, const void* dout,
                                               const float* dlse, void* dq, void* dk, void* dv,
                                               void* dk_extra, void* dv_extra, void* stream);
+
+/*
+ * Halo transport between the GPUs of one box for a volume sharded along its
+ * leading axis (one process per GPU).  The reference is single-device and has
+ * no counterpart; these two calls let the window of a query reach key/value
+ * planes owned by the neighbouring rank, so that the sharded result equals
+ * the reference's unsharded one (src/natten_mlx/functional.py:340-383).
+ *
+ * natten_b200_peer_copy2d copies `rows` rows of `width_bytes` bytes between
+ * pitched buffers with plain 16-byte loads and stores; dst or src may be
+ * another GPU's memory mapped into this process (CUDA IPC, symmetric memory).
+ * Addresses, pitches and the width are multiples of 16 bytes.
+ *
+ * natten_b200_peer_barrier orders such copies between ranks on their streams:
+ * flag_blocks (host array, `world` entries) holds the address, as mapped in
+ * this process, of every rank's flag block (`world` zero-initialised uint32
+ * words in peer-mapped memory).  The kernel publishes `epoch` in every peer's
+ * block and waits until every peer has published an epoch >= it in this
+ * rank's block; work queued on the stream after it sees what the peers wrote
+ * before their barrier.  Epochs of successive barriers on one set of blocks
+ * increase.  A wait longer than timeout_ms (0 = 10 s) gives up and sets
+ * natten_b200_kernel_status() to 2 instead of spinning on.
+ */
+int natten_b200_peer_copy2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                            size_t width_bytes, size_t rows, void* stream);
+int natten_b200_peer_barrier(const uint64_t* flag_blocks, int32_t world, int32_t rank, uint32_t epoch,
+                             uint32_t timeout_ms, void* stream);
 
 /*
  * Merge two attention results over the same queries:

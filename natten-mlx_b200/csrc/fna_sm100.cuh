@@ -18,6 +18,8 @@ size_t fused_backward_scratch_sm100(const Geo& g, int dtype);
 // 1 when a tensor-core kernel on the current device gave up on a wait since
 // the last call (synchronises with the device and clears the flag).
 int sm100_read_status();
+// Device address of the status word of the current device (nullptr without a device).
+int* sm100_status_word();
 // Diagnostic builds (-DNB_SM100_PROFILE): buffer that receives the kernels' cycle counters.
 void sm100_set_profile_buffer(float* ptr);
 // Text description of the tiling chosen for a geometry (no GPU needed).

@@ -74,6 +74,8 @@ SYMBOLS = {
     "natten_b200_static_scratch_capacity": (ctypes.c_size_t, []),
     "natten_b200_fused_backward_static_scratch": (ctypes.c_int, [_G] + [_P] * 15),
     "natten_b200_kernel_status": (ctypes.c_int, []),
+    "natten_b200_peer_copy2d": (ctypes.c_int, [_P, ctypes.c_size_t, _P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, _P]),
+    "natten_b200_peer_barrier": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint32, _P]),
     "natten_b200_describe_plan": (ctypes.c_int, [_G, ctypes.c_char_p, ctypes.c_size_t]),
     "natten_b200_plan_hint": (ctypes.c_int, [_G, ctypes.c_int32, _P, ctypes.c_int32]),
     "natten_b200_merge_forward": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32] + [_P] * 7),

@@ -3,10 +3,13 @@ volume can also be split along its leading spatial axis, with a K/V halo
 exchange in the forward and the reverse dK/dV halo reduction in the backward.
 
 The reference is single-device (it has no distributed code); this module is
-what makes its operators span the GPUs of one box.  One process per GPU,
-``torch.distributed`` point-to-point (NCCL send/recv over NVLink on GPUs, gloo
-in the CPU tests).  Halo planes are received into local memory before any
-kernel reads them.
+what makes its operators span the GPUs of one box.  One process per GPU.  Two
+transports move the halo planes: on GPUs under an NCCL group the library's own
+copy kernel writes them straight into the consumer's K/V buffer over NVLink
+(buffers in symmetric memory, ordered by the library's flag barrier; see
+``PeerTransport``); otherwise ``torch.distributed`` point-to-point (gloo in the
+CPU tests, NCCL send/recv when asked for).  Either way halo planes are in
+local memory before any kernel reads them.
 
 Window positions are evaluated in global coordinates: each rank passes its
 slab offsets to the kernels (``Slab``), so results equal the unsharded call.
@@ -17,9 +20,13 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
+import ctypes
+import warnings
+
 import torch
 import torch.distributed as dist
 
+from . import _lib
 from ._core import cuda as _cuda
 from .utils import window as _window
 
@@ -200,6 +207,305 @@ def reduce_halo_grads(grad_buf: torch.Tensor, plans: Sequence[SlabPlan], rank: i
     return reduce_halo_grads_many([grad_buf], plans, rank, group, axis)[0]
 
 
+def halo_transfers(plans: Sequence[SlabPlan]) -> List[Tuple[int, int, int, int]]:
+    """Every (owner, borrower, lo, hi): planes [lo, hi) owned by ``owner`` that ``borrower``'s queries address."""
+    out = []
+    for owner in plans:
+        for other in plans:
+            if other.rank == owner.rank:
+                continue
+            lo, hi = _overlap(owner.q_lo, owner.q_hi, other.kv_lo, other.kv_hi)
+            if hi > lo:
+                out.append((owner.rank, other.rank, lo, hi))
+    return out
+
+
+def staging_layout(plans: Sequence[SlabPlan]) -> Tuple[dict, int]:
+    """Where an owner keeps the gradient partials it receives: {(owner, borrower): first plane of that borrower's
+    range in the owner's staging area}, and the number of planes the largest staging area holds."""
+    offsets, used = {}, [0] * len(plans)
+    for owner, borrower, lo, hi in halo_transfers(plans):
+        offsets[(owner, borrower)] = used[owner]
+        used[owner] += hi - lo
+    return offsets, max(used) if used else 0
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Lease:
+    """One symmetric allocation handed out by a ``PeerTransport``; goes back to its pool on ``release`` (or when
+    the last reference dies).
+
+    ``read_epoch`` is the transport's barrier count when a kernel reading the allocation was last queued on this
+    rank's stream (``mark_read``).  Another rank may write into the allocation once a barrier queued after that
+    point has completed; ``needs_barrier`` tells whether such a barrier has been queued yet.  Every rank makes
+    the same calls in the same order, so every rank reaches the same answer."""
+
+    def __init__(self, transport, nbytes, tensor, ptrs, read_epoch=-1):
+        self.transport, self.nbytes, self.tensor, self.ptrs = transport, nbytes, tensor, ptrs
+        self.read_epoch = read_epoch
+        self.persistent = False
+        self.live = True
+
+    def mark_read(self):
+        self.read_epoch = self.transport.epoch
+
+    def needs_barrier(self) -> bool:
+        return self.transport.epoch <= self.read_epoch
+
+    def release(self):
+        if self.live:
+            self.live = False
+            for key in [k for k, v in _kv_registry.items() if v[0] is self]:
+                del _kv_registry[key]
+            self.transport._pool.setdefault(self.nbytes, []).append((self.tensor, self.ptrs, self.read_epoch))
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+_kv_registry = {}      # (data_ptr, shape) of a tensor handed out by peer_kv_buffers -> (lease, index)
+
+
+class PeerTransport:
+    """Halo transport of one process group over peer memory.
+
+    Buffers come from ``torch.distributed._symmetric_memory`` (every rank's allocation is mapped into every other
+    rank's address space); the data is moved by the library's copy kernel (``natten_b200_peer_copy2d``: plain
+    16-byte stores into the consumer's memory) and ordered by its flag barrier (``natten_b200_peer_barrier``,
+    bounded waits).  All ranks of the group must make the same sequence of calls, on one stream each; allocations
+    are collective and are kept in a pool, so steady-state steps allocate nothing."""
+
+    def __init__(self, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self._symm = symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._pool = {}
+        self.epoch = 0
+        flags = symm.empty(64, dtype=torch.int32, device=self.device)
+        flags.zero_()
+        torch.cuda.synchronize(self.device)
+        self._flags = flags
+        self._flag_handle = symm.rendezvous(flags, self.group)
+        self._flag_ptrs = (ctypes.c_uint64 * self.world)(*[int(p) for p in self._flag_handle.buffer_ptrs])
+        dist.barrier(self.group)              # every rank's flag block is zero before anyone publishes into it
+
+    def barrier(self):
+        """Queue a barrier over the ranks on the current stream."""
+        self.epoch += 1
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.load().natten_b200_peer_barrier(self._flag_ptrs, self.world, self.rank, self.epoch, 0,
+                                                        ctypes.c_void_p(stream)))
+
+    def acquire(self, nbytes: int) -> _Lease:
+        """A symmetric allocation of ``nbytes`` (the same on every rank; collective when the pool has none)."""
+        free = self._pool.get(nbytes)
+        if free:
+            tensor, ptrs, read_epoch = free.pop()
+            return _Lease(self, nbytes, tensor, ptrs, read_epoch)
+        tensor = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        handle = self._symm.rendezvous(tensor, self.group)
+        return _Lease(self, nbytes, tensor, [int(p) for p in handle.buffer_ptrs])
+
+    def copy2d(self, dst_ptr, dst_pitch, src_ptr, src_pitch, width, rows):
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(_lib.load().natten_b200_peer_copy2d(ctypes.c_void_p(dst_ptr), dst_pitch, ctypes.c_void_p(src_ptr),
+                                                       src_pitch, width, rows, ctypes.c_void_p(stream)))
+
+
+_transports = {}
+_transport_refused = {}
+
+
+def peer_transport(group=None) -> Optional[PeerTransport]:
+    """The group's ``PeerTransport`` (created on first use, collectively), or None where symmetric memory cannot
+    be set up (the reason is kept in a warning); callers then use point-to-point transfers."""
+    key = group if group is not None else dist.group.WORLD
+    if key in _transports:
+        return _transports[key]
+    if key in _transport_refused:
+        return None
+    try:
+        _transports[key] = PeerTransport(group)
+    except (RuntimeError, ImportError, AttributeError) as err:
+        _transport_refused[key] = str(err)
+        warnings.warn(f"peer-memory halo transport unavailable, using send/recv: {err}")
+        return None
+    return _transports[key]
+
+
+def _use_peer(tensor: torch.Tensor, group, transport: str) -> bool:
+    if transport == "p2p":
+        return False
+    ok = (tensor.is_cuda and dist.get_backend(group) == "nccl" and dist.get_world_size(group) > 1
+          and _plane_bytes(tensor, 1) % 16 == 0 and tensor.data_ptr() % 16 == 0)
+    if transport == "peer" and not ok:
+        raise ValueError("the peer-memory transport needs CUDA tensors whose planes are multiples of 16 bytes and an "
+                         "NCCL group of more than one rank")
+    if not ok:
+        return False
+    t = peer_transport(group)
+    if t is None and transport == "peer":
+        raise RuntimeError(f"peer-memory transport unavailable: {_transport_refused.get(group if group is not None else dist.group.WORLD)}")
+    return t is not None
+
+
+def _plane_bytes(t: torch.Tensor, axis: int) -> int:
+    n = t.element_size()
+    for x in t.shape[axis + 1:]:
+        n *= x
+    return n
+
+
+def _kv_layout(shapes_dtypes, plans, axis):
+    """Byte offset of every tensor's buffer inside one allocation, and the allocation's size: each buffer has room
+    for the widest [kv_lo, kv_hi) range of any rank, so that the layout is the same on every rank."""
+    span = max(p.kv_hi - p.kv_lo for p in plans)
+    offs, total = [], 0
+    for shape, dtype in shapes_dtypes:
+        n = torch.empty((), dtype=dtype).element_size() * span
+        for i, x in enumerate(shape):
+            if i != axis:
+                n *= x
+        offs.append(total)
+        total += _align(n)
+    return offs, total
+
+
+def _buffer_view(lease, off, local_shape, dtype, me, axis):
+    shape = list(local_shape)
+    shape[axis] = me.kv_hi - me.kv_lo
+    n = torch.empty((), dtype=dtype).element_size()
+    for x in shape:
+        n *= x
+    return lease.tensor[off: off + n].view(dtype).view(shape)
+
+
+def peer_kv_buffers(local_shape, dtype, plans: Sequence[SlabPlan], rank: int, count: int = 2, group=None, axis: int = 1):
+    """``count`` tensors of ``local_shape`` (K, V, ...) for this rank's planes that live inside one symmetric
+    allocation, each with room for its halo planes around it: (tensors, lease).  A caller that produces its K/V
+    into them saves ``na_sharded`` the copy of the owned planes into a halo buffer (the neighbours' planes are
+    written around them in place).  Collective.  ``lease.release()`` gives the memory back."""
+    t = peer_transport(group)
+    if t is None:
+        raise RuntimeError("peer-memory transport unavailable")
+    me = plans[rank]
+    offs, total = _kv_layout([(local_shape, dtype)] * count, plans, axis)
+    lease = t.acquire(total)
+    lease.persistent = True
+    out = []
+    for i in range(count):
+        own = _buffer_view(lease, offs[i], local_shape, dtype, me, axis).narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo)
+        _kv_registry[(own.data_ptr(), tuple(own.shape))] = (lease, i)
+        out.append(own)
+    return out, lease
+
+
+def _registered(locals_):
+    """The lease whose buffers ``locals_`` are, in order (see ``peer_kv_buffers``), or None."""
+    lease = None
+    for i, x in enumerate(locals_):
+        hit = _kv_registry.get((x.data_ptr(), tuple(x.shape)))
+        if hit is None or hit[1] != i or (lease is not None and hit[0] is not lease):
+            return None
+        lease = hit[0]
+    return lease
+
+
+def exchange_halos_peer(locals_: Sequence[torch.Tensor], plans: Sequence[SlabPlan], rank: int, group=None,
+                        axis: int = 1):
+    """``exchange_halos`` over peer memory: (buffers, lease).  Every rank writes the planes its neighbours need
+    straight into their buffers, then a barrier tells everyone that its planes have arrived (a barrier before
+    the writes is only queued when none has been queued since the buffers were last read).  The buffers are
+    views of the lease's allocation; the caller calls ``lease.mark_read()`` after queueing the kernels that read
+    them and, unless the lease is persistent, ``lease.release()`` when nothing reads them any more."""
+    t = peer_transport(group)
+    me = plans[rank]
+    rows = 1
+    for x in locals_[0].shape[:axis]:
+        rows *= x
+    pb = [_plane_bytes(x, axis) for x in locals_]
+    offs, total = _kv_layout([(x.shape, x.dtype) for x in locals_], plans, axis)
+    lease = _registered(locals_)
+    if lease is None:
+        lease = t.acquire(total)
+        locals_ = [x if x.is_contiguous() else x.contiguous() for x in locals_]
+        pitch = [(me.q_hi - me.q_lo) * b for b in pb]
+    else:
+        pitch = [(me.kv_hi - me.kv_lo) * b for b in pb]       # the owned planes already sit inside the buffers
+    if lease.needs_barrier():
+        t.barrier()                               # nobody still reads the buffers the writes below go to
+    transfers = [x for x in halo_transfers(plans) if x[0] == rank]
+    for i, local in enumerate(locals_):           # what the neighbours wait for goes first
+        for _, borrower, lo, hi in transfers:
+            other = plans[borrower]
+            t.copy2d(lease.ptrs[borrower] + offs[i] + (lo - other.kv_lo) * pb[i], (other.kv_hi - other.kv_lo) * pb[i],
+                     local.data_ptr() + (lo - me.q_lo) * pb[i], pitch[i], (hi - lo) * pb[i], rows)
+    bufs = []
+    for i, local in enumerate(locals_):
+        buf = _buffer_view(lease, offs[i], local.shape, local.dtype, me, axis)
+        if not lease.persistent:
+            buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo).copy_(local)
+        bufs.append(buf)
+    t.barrier()                                   # the planes others wrote into this rank's buffers have arrived
+    return bufs, lease
+
+
+def reduce_halo_grads_peer(grad_bufs: Sequence[torch.Tensor], plans: Sequence[SlabPlan], rank: int, group=None,
+                           axis: int = 1) -> List[torch.Tensor]:
+    """``reduce_halo_grads_many`` over peer memory: partial sums are written into the owner's staging area, the
+    owner adds them into its planes."""
+    t = peer_transport(group)
+    me = plans[rank]
+    rows = 1
+    for x in grad_bufs[0].shape[:axis]:
+        rows *= x
+    pb = [_plane_bytes(x, axis) for x in grad_bufs]
+    where, span = staging_layout(plans)
+    offs, total = [], 0
+    for b in pb:
+        offs.append(total)
+        total += _align(rows * span * b)
+    owns = [g.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo) for g in grad_bufs]
+    if total == 0:
+        return owns
+    lease = t.acquire(total)
+    transfers = halo_transfers(plans)
+    if lease.needs_barrier():
+        t.barrier()                               # the owners have finished with what the last call left there
+    for i, g in enumerate(grad_bufs):
+        for owner, borrower, lo, hi in transfers:
+            if borrower != rank:
+                continue
+            # the owner's area holds rows of (hi - lo) planes for this borrower, densely: pitch = width
+            t.copy2d(lease.ptrs[owner] + offs[i] + where[(owner, borrower)] * rows * pb[i], (hi - lo) * pb[i],
+                     g.data_ptr() + (lo - me.kv_lo) * pb[i], (me.kv_hi - me.kv_lo) * pb[i], (hi - lo) * pb[i], rows)
+    t.barrier()                                   # the partials for this rank's planes have arrived
+    for i, own in enumerate(owns):
+        for owner, borrower, lo, hi in transfers:
+            if owner != rank:
+                continue
+            shape = list(own.shape)
+            shape[axis] = hi - lo
+            n = 1
+            for x in shape:
+                n *= x
+            start = offs[i] + where[(owner, borrower)] * rows * pb[i]
+            piece = lease.tensor[start: start + n * own.element_size()].view(own.dtype).view(shape)
+            own.narrow(axis, lo - me.q_lo, hi - lo).add_(piece)
+    lease.mark_read()
+    lease.release()
+    return owns
+
+
 def _global_rank(group_rank: int, group) -> int:
     if group is None:
         return group_rank
@@ -224,34 +530,55 @@ def fused_slab_forward_backward(q, k_buf, v_buf, grad_out, plan: SlabPlan, exten
 
 class _ShardedNA(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, extent, ks, dl, ca, scale, plans, rank, group):
-        k_buf, v_buf = exchange_halos([k, v], plans, rank, group)
+    def forward(ctx, q, k, v, extent, ks, dl, ca, scale, plans, rank, group, transport):
+        peer = _use_peer(q, group, transport)
+        lease = None
+        if peer:
+            (k_buf, v_buf), lease = exchange_halos_peer([k, v], plans, rank, group)
+        else:
+            k_buf, v_buf = exchange_halos([k, v], plans, rank, group)
         slab = _slab(plans[rank], extent)
         one = (1,) * len(extent)
         out, lse = _cuda.fused_forward(q, k_buf, v_buf, ks, one, dl, ca, scale, slab=slab)
+        if lease is not None:
+            lease.mark_read()
+            if not lease.persistent and not any(ctx.needs_input_grad[:3]):
+                lease.release()               # nothing is saved for a backward
+                lease = None
         ctx.save_for_backward(q, k_buf, v_buf, out, lse)
-        ctx.args = (extent, ks, dl, ca, scale, plans, rank, group, slab, one)
+        ctx.lease = lease
+        ctx.args = (extent, ks, dl, ca, scale, plans, rank, group, slab, one, peer)
         return out, lse
 
     @staticmethod
     def backward(ctx, grad_out, grad_lse):
         q, k_buf, v_buf, out, lse = ctx.saved_tensors
-        extent, ks, dl, ca, scale, plans, rank, group, slab, one = ctx.args
+        extent, ks, dl, ca, scale, plans, rank, group, slab, one, peer = ctx.args
         if grad_out is None:
             grad_out = torch.zeros_like(out)
         dq, dk, dv, _, _ = _cuda.fused_backward(q, k_buf, v_buf, out, lse, grad_out, grad_lse, ks, one, dl, ca,
                                                 scale, slab=slab)
-        dk, dv = reduce_halo_grads_many([dk, dv], plans, rank, group)
-        return (dq, dk, dv) + (None,) * 8
+        if ctx.lease is not None:
+            ctx.lease.mark_read()
+            if not ctx.lease.persistent:
+                ctx.lease.release()
+            ctx.lease = None
+        if peer:
+            dk, dv = reduce_halo_grads_peer([dk, dv], plans, rank, group)
+        else:
+            dk, dv = reduce_halo_grads_many([dk, dv], plans, rank, group)
+        return (dq, dk, dv) + (None,) * 9
 
 
 def na_sharded(query, key, value, global_extent: int, kernel_size, dilation=1, is_causal=False,
-               scale: Optional[float] = None, return_lse: bool = False, group=None):
+               scale: Optional[float] = None, return_lse: bool = False, group=None, transport: str = "auto"):
     """Neighborhood attention on a volume sharded along its leading spatial axis.
 
     Each rank passes its own planes of q/k/v (``[B, T_local, ..., H, D]``, the
     contiguous balanced split of ``global_extent`` planes, see ``shard_bounds``).
-    Stride is 1.  Returns this rank's planes of the output (and LSE)."""
+    Stride is 1.  ``transport``: "peer" (the library's copy kernel over peer memory), "p2p" (point-to-point
+    send/recv of the group's backend) or "auto" (peer on GPUs under NCCL, else p2p).  Returns this rank's planes
+    of the output (and LSE)."""
     rank_nd = query.dim() - 3
     tup = lambda x: tuple(x) if isinstance(x, (tuple, list)) else (x,) * rank_nd
     ks, dl, ca = tup(kernel_size), tup(dilation), tuple(bool(c) for c in tup(is_causal))
@@ -262,5 +589,7 @@ def na_sharded(query, key, value, global_extent: int, kernel_size, dilation=1, i
         raise ValueError(f"rank {me} must hold planes [{plans[me].q_lo}, {plans[me].q_hi}) of the leading axis")
     extent = (global_extent,) + tuple(query.shape[2:2 + rank_nd - 1])
     scale_value = query.shape[-1] ** -0.5 if scale is None else float(scale)
-    out, lse = _ShardedNA.apply(query, key, value, extent, ks, dl, ca, scale_value, plans, me, group)
+    if transport not in ("auto", "peer", "p2p"):
+        raise ValueError(f"transport must be 'auto', 'peer' or 'p2p', got {transport!r}")
+    out, lse = _ShardedNA.apply(query, key, value, extent, ks, dl, ca, scale_value, plans, me, group, transport)
     return (out, lse) if return_lse else out

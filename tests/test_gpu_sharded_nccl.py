@@ -1,4 +1,5 @@
-"""Leading-axis sharding with the K/V halo exchange on real GPUs (NCCL point-to-point):
+"""Leading-axis sharding with the K/V halo exchange on real GPUs, over both transports (the
+library's copy kernel writing into the neighbour's symmetric memory, and NCCL point-to-point):
 every rank holds its planes of a 3-D volume, calls ``sharding.na_sharded`` forward and
 backward, and its planes of the output and of dq/dk/dv must equal the unsharded result of the
 same kernels on one GPU.  Needs two or more GPUs; on a single-GPU box the test is skipped (the
@@ -30,23 +31,47 @@ def _worker(rank, world, port, causal, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import natten_mlx_b200 as nb
-        from natten_mlx_b200 import sharding
+        from natten_mlx_b200 import _lib, sharding
         T, ks, dl, ca = 12, (3, 3, 5), (2, 1, 1), (causal, False, False)
         gen = torch.Generator().manual_seed(21)
         full = [torch.randn((2, T, 6, 9, 2, 16), generator=gen) for _ in range(4)]      # q, k, v, cotangent (two samples: halo planes travel per sample)
         bounds = sharding.shard_bounds(T, world)
         lo, hi = bounds[rank], bounds[rank + 1]
         dev = torch.device("cuda", rank)
-        q, k, v = (t[:, lo:hi].to(dev).requires_grad_(True) for t in full[:3])
-        out = sharding.na_sharded(q, k, v, T, ks, dl, ca)
-        out.backward(full[3][:, lo:hi].to(dev))
         # the unsharded result on this rank's GPU
         qf, kf, vf = (t.to(dev).requires_grad_(True) for t in full[:3])
         ref = nb.na3d(qf, kf, vf, kernel_size=ks, dilation=dl, is_causal=ca)
         ref.backward(full[3].to(dev))
-        ok = [torch.allclose(out, ref[:, lo:hi], atol=1e-5, rtol=1e-5)]
-        for a, b in ((q, qf), (k, kf), (v, vf)):
-            ok.append(torch.allclose(a.grad, b.grad[:, lo:hi], atol=1e-4, rtol=1e-4))
+        ok = []
+        # the peer transport twice: the second step reuses the pooled buffers and the next barrier epochs
+        for transport in ("peer", "peer", "p2p"):
+            q, k, v = (t[:, lo:hi].to(dev).requires_grad_(True) for t in full[:3])
+            out = sharding.na_sharded(q, k, v, T, ks, dl, ca, transport=transport)
+            out.backward(full[3][:, lo:hi].to(dev))
+            ok.append(torch.allclose(out, ref[:, lo:hi], atol=1e-5, rtol=1e-5))
+            for a, b in ((q, qf), (k, kf), (v, vf)):
+                ok.append(torch.allclose(a.grad, b.grad[:, lo:hi], atol=1e-4, rtol=1e-4))
+        # K and V produced straight into symmetric memory (no copy of the owned planes), two steps
+        plans = sharding.all_plans(T, world, ks[0], dl[0], ca[0])
+        (kp, vp), kv_lease = sharding.peer_kv_buffers((2, hi - lo, 6, 9, 2, 16), torch.float32, plans, rank)
+        kp.copy_(full[1][:, lo:hi])
+        vp.copy_(full[2][:, lo:hi])
+        kp.requires_grad_(True)
+        vp.requires_grad_(True)
+        for _ in range(2):
+            q = full[0][:, lo:hi].to(dev).requires_grad_(True)
+            out = sharding.na_sharded(q, kp, vp, T, ks, dl, ca, transport="peer")
+            gq, gk, gv = torch.autograd.grad(out, (q, kp, vp), full[3][:, lo:hi].to(dev))
+            ok.append(torch.allclose(out, ref[:, lo:hi], atol=1e-5, rtol=1e-5))
+            for a, b in ((gq, qf), (gk, kf), (gv, vf)):
+                ok.append(torch.allclose(a, b.grad[:, lo:hi], atol=1e-4, rtol=1e-4))
+        kv_lease.release()
+        ok.append(_lib.kernel_status() == 0)          # no barrier gave up on its wait
+        with torch.no_grad():                          # nothing saved: the buffers go straight back to the pool
+            q, k, v = (t[:, lo:hi].to(dev) for t in full[:3])
+            ok.append(torch.allclose(sharding.na_sharded(q, k, v, T, ks, dl, ca, transport="peer"), ref[:, lo:hi],
+                                     atol=1e-5, rtol=1e-5))
+        ok.append(len(sharding.peer_transport()._pool) > 0)
         results[rank] = tuple(bool(x) for x in ok)
     finally:
         dist.destroy_process_group()
@@ -61,4 +86,4 @@ def test_na_sharded_matches_unsharded_over_nccl(causal):
     mp.spawn(_worker, args=(world, _free_port(), causal, results), nprocs=world, join=True)
     assert len(results) == world
     for r in range(world):
-        assert results[r] == (True, True, True, True), (r, results[r])
+        assert all(results[r]) and len(results[r]) == 23, (r, results[r])
