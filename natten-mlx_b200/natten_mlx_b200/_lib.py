@@ -138,7 +138,8 @@ def trace_report() -> dict:
 
 
 def kernel_status() -> int:
-    """1 if a tensor-core kernel gave up on a wait since the last call (synchronises)."""
+    """Non-zero if a kernel gave up on a bounded wait since the last call (1 a tensor-core kernel, 2 a peer
+    barrier); synchronises with the device."""
     return int(load().natten_b200_kernel_status())
 
 
