@@ -623,7 +623,11 @@ def run_table_workload(args):
         def step():
             out = nb.na2d_varlen(q, k, v, st, 13, 2, additional_keys=ak, additional_values=av, host_sizes=host_sizes)
             return torch.autograd.grad(out, (q, k, v, ak, av), cot)
-        eager, extra_cfg = None, {}
+        eager = None
+        # the tilings of the three tensor-core kernels are measured once for this geometry and pinned
+        res = nb.tune.tune_fused(q.detach(), k.detach(), v.detach(), 13, 2, sizes=st, host_sizes=host_sizes,
+                                 additional_keys=ak.detach(), additional_values=av.detach())
+        extra_cfg = {"tuned": {kn: {"tile": list(t), "max_cols": c} for kn, (t, c, _) in res.items()}}
         dtype = "bf16"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(max(args.warmup, 3)):

@@ -32,10 +32,13 @@ def _tile_shapes(rank: int, rows: int):
 
 
 def tune_fused(query, key, value, kernel_size, dilation=1, is_causal=False, scale: Optional[float] = None,
-               max_cols: Sequence[int] = (0, 256, 192, 128, 96, 80, 64, 48), repeats: int = 3, verbose: bool = False
+               max_cols: Sequence[int] = (0, 256, 192, 128, 96, 80, 64, 48), repeats: int = 3, verbose: bool = False,
+               sizes=None, host_sizes=None, additional_keys=None, additional_values=None
                ) -> Dict[str, Tuple[Tuple[int, ...], int, float]]:
     """Times candidate tilings of the fused forward and backward for these tensors and pins the best.
 
+    ``sizes`` / ``host_sizes`` (per-sample extents on the device and their host copy) and the extra tokens
+    describe a variable-size call; the pinned tilings apply to calls of exactly that geometry.
     Returns ``{kernel name: (tile, max_cols, milliseconds)}`` of the winners.  Shapes the tensor-core
     kernels do not take are left alone (empty result)."""
     rank = query.dim() - 3
@@ -46,9 +49,15 @@ def tune_fused(query, key, value, kernel_size, dilation=1, is_causal=False, scal
     if not query.is_cuda or query.dtype not in (torch.float16, torch.bfloat16):
         return {}
     sc = query.shape[-1] ** -0.5 if scale is None else float(scale)
+    n_extra = 0 if additional_keys is None else int(additional_keys.shape[1])
+    if sizes is not None:
+        sizes = backend._sizes_tensor(sizes, query.shape[0], rank, query.device)
+        host_sizes = backend._host_sizes(sizes, host_sizes, query.shape[0], rank)
     geom = _lib.make_geom(rank, query.shape[0], query.shape[-2], key.shape[-2], query.shape[-1],
                           {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16}[query.dtype],
-                          tuple(query.shape[1:1 + rank]), ks, one, dl, [int(c) for c in ca], sc)
+                          tuple(query.shape[1:1 + rank]), ks, one, dl, [int(c) for c in ca], sc, n_extra=n_extra,
+                          extents_ptr=0 if sizes is None else sizes.data_ptr(),
+                          host_extents=None if sizes is None else host_sizes)
     try:
         if "unsupported" in _lib.describe_plan(geom):
             return {}
@@ -64,8 +73,9 @@ def tune_fused(query, key, value, kernel_size, dilation=1, is_causal=False, scal
         return lib.natten_b200_plan_hint(geom, kernel, arr, int(cols))
 
     def run_once():
-        out, lse = backend.fused_forward(query, key, value, ks, one, dl, ca, sc, path="tcgen05")
-        backend.fused_backward(query, key, value, out, lse, cot, None, ks, one, dl, ca, sc, path="tcgen05")
+        extra = dict(k_extra=additional_keys, v_extra=additional_values, sizes=sizes, host_sizes=host_sizes)
+        out, lse = backend.fused_forward(query, key, value, ks, one, dl, ca, sc, path="tcgen05", **extra)
+        backend.fused_backward(query, key, value, out, lse, cot, None, ks, one, dl, ca, sc, path="tcgen05", **extra)
 
     def measure():
         run_once()                                     # warm: attribute setting, plan building, caches
