@@ -53,3 +53,28 @@ def test_plan_hint_set_refuse_release():
     assert lib.natten_b200_plan_hint(g, 3, None, 0) == _lib.EINVAL
     assert lib.natten_b200_plan_hint(g, 0, None, 0) == _lib.OK
     assert _lib.describe_plan(g) == auto
+
+
+def test_tuned_plans_of_a_variable_size_batch_with_extra_tokens_keep_parity():
+    sizes = [(24, 20), (16, 28)]
+    q = _rand((2, 24, 28, 4, 32), 11)
+    k, v = _rand((2, 24, 28, 2, 32), 12), _rand((2, 24, 28, 2, 32), 13)
+    ak, av = _rand((2, 6, 2, 32), 14), _rand((2, 6, 2, 32), 15)
+    cot = _rand((2, 24, 28, 4, 32), 16)
+    ks, dl = (5, 3), (1, 2)
+    ref = lambda *t: oracle.na_varlen(t[0], t[1], t[2], sizes, ks, dl, additional_keys=t[3], additional_values=t[4])
+    o_ref, g_ref = oracle.grads(ref, [t.float() for t in (q, k, v, ak, av)], cot.float())
+    dev = [t.to(DEV) for t in (q, k, v, ak, av)]
+    st = torch.tensor(sizes, dtype=torch.int32, device=DEV)
+    res = nb.tune.tune_fused(dev[0], dev[1], dev[2], ks, dilation=dl, max_cols=(0, 96, 48), repeats=1, sizes=st,
+                             host_sizes=sizes, additional_keys=dev[3], additional_values=dev[4])
+    assert set(res) == {"fna_fwd_sm100", "fna_bwd_dq_sm100", "fna_bwd_dkv_sm100"}
+    leaves = [t.requires_grad_(True) for t in dev]
+    out = nb.na2d_varlen(*leaves[:3], st, ks, dl, additional_keys=leaves[3], additional_values=leaves[4], host_sizes=sizes)
+    assert _lib.last_path() == "tcgen05"
+    grads = torch.autograd.grad(out, leaves, cot.to(DEV))
+    assert _lib.kernel_status() == 0
+    rel = lambda a, b: float((a.detach().float().cpu() - b).abs().max() / b.abs().max())
+    assert rel(out, o_ref) < 2e-2
+    for a, b in zip(grads, g_ref):
+        assert rel(a, b) < 2e-2
