@@ -803,6 +803,81 @@ def run_tshard(args, rank, world, local_rank):
         "clocks": clocks}))
 
 
+# ---------------------------------------------------------------------------
+# the variable-size GQA batch with extra tokens over several GPUs: whole samples per rank, balanced by token
+# count, no collective on the data path
+# ---------------------------------------------------------------------------
+def run_varlen_sharded(args, rank, world, local_rank):
+    import torch.distributed as dist
+    import natten_mlx_b200 as nb
+    from natten_mlx_b200 import _lib, sharding
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    B, M, Hq, Hkv, D, NX = 16, 128, 16, 4, 128, 64
+    gen = torch.Generator().manual_seed(1236)
+    sizes = (torch.randint(0, 9, (B, 2), generator=gen) * 8 + 64).to(torch.int32)     # the same draw as on one GPU
+    host_all = [tuple(int(x) for x in r) for r in sizes.tolist()]
+    parts = sharding.balance_by_tokens(host_all, world)
+    mine = parts[rank]
+    host_sizes = [host_all[i] for i in mine]
+    n = len(mine)
+    gen = torch.Generator().manual_seed(2236 + rank)
+    bf = torch.bfloat16
+    rnd = lambda shape: torch.randn(shape, generator=gen, dtype=torch.float32).to(bf).to(dev)
+    q = rnd((n, M, M, Hq, D)).requires_grad_(True)
+    k, v = (rnd((n, M, M, Hkv, D)).requires_grad_(True) for _ in range(2))
+    ak, av = (rnd((n, NX, Hkv, D)).requires_grad_(True) for _ in range(2))
+    cot = rnd((n, M, M, Hq, D))
+    st = torch.tensor(host_sizes, dtype=torch.int32, device=dev)
+    nb.tune.tune_fused(q.detach(), k.detach(), v.detach(), 13, 2, sizes=st, host_sizes=host_sizes,
+                       additional_keys=ak.detach(), additional_values=av.detach())
+
+    def step():
+        out = nb.na2d_varlen(q, k, v, st, 13, 2, additional_keys=ak, additional_values=av, host_sizes=host_sizes)
+        return torch.autograd.grad(out, (q, k, v, ak, av), cot)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    dist.barrier()
+    torch.cuda.synchronize()
+    count0 = _lib.launch_count()
+    for a, b in evs:
+        flush.zero_()
+        a.record()
+        step()
+        b.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    launches = _lib.launch_count() - count0
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs) / args.steps], device=dev)
+    per_rank = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(per_rank, t)
+    ms = max(float(x.item()) for x in per_rank)
+    clocks = sampler.stop() if rank == 0 else None
+    if _lib.kernel_status() != 0:
+        raise RuntimeError("a bounded wait of a kernel ran out during the timed region")
+    if rank != 0:
+        return
+    tokens = [sum(host_all[i][0] * host_all[i][1] for i in p) for p in parts]
+    flops = 3.5 * 4.0 * Hq * sum(tokens) * (169 + NX) * D
+    print(json.dumps({
+        "metric": "na_fwd_bwd_effective_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"na2d bf16 varlen B=16 max 128x128 ({sum(tokens)} tokens) 16q/4kv heads D=128 K=13x13 dilation 2, "
+                               f"64 extra tokens, lse+merge, fwd+bwd; whole samples per rank, balanced by tokens, no collective",
+                   "samples_per_rank": [len(p) for p in parts], "tokens_per_rank": tokens,
+                   "ms_per_step_per_rank": [float(x.item()) for x in per_rank],
+                   "l2": "256 MiB buffer written between timed iterations", "kernel_family": _lib.last_path()},
+        "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": int(launches), "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -836,8 +911,19 @@ def main():
                 dist.destroy_process_group()
         return
     if args.workload in TABLE_WORKLOADS:
+        world = int(os.environ.get("WORLD_SIZE", "1"))
         if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "table workloads have no reference arm"}))
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "table workloads have no reference arm"}))
+        elif args.workload == "na2d_varlen_gqa" and world > 1:
+            import torch.distributed as dist
+            local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            try:
+                run_varlen_sharded(args, int(os.environ.get("RANK", "0")), world, local_rank)
+            finally:
+                dist.destroy_process_group()
         elif int(os.environ.get("RANK", "0")) == 0:
             run_table_workload(args)
         return

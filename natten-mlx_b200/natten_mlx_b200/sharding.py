@@ -67,6 +67,27 @@ def all_plans(extent: int, world: int, kernel: int, dilation: int, causal) -> Li
     return [slab_plan(extent, world, r, kernel, dilation, causal) for r in range(world)]
 
 
+def balance_by_tokens(sizes: Sequence[Sequence[int]], world: int) -> List[List[int]]:
+    """Samples of a variable-size batch for each rank, balanced by token count (the product of a sample's
+    extents) rather than by sample count: largest sample first onto the lightest rank.  Every rank gets at
+    least one sample when there are enough; the lists hold sample indices in ascending order."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    tokens = []
+    for i, s in enumerate(sizes):
+        n = 1
+        for x in (s if isinstance(s, (list, tuple)) else (s,)):
+            n *= int(x)
+        tokens.append((n, i))
+    load = [0] * world
+    out: List[List[int]] = [[] for _ in range(world)]
+    for n, i in sorted(tokens, key=lambda t: (-t[0], t[1])):
+        r = min(range(world), key=lambda j: (load[j], len(out[j]), j))
+        out[r].append(i)
+        load[r] += n
+    return [sorted(x) for x in out]
+
+
 def _overlap(a_lo, a_hi, b_lo, b_hi) -> Tuple[int, int]:
     lo, hi = max(a_lo, b_lo), min(a_hi, b_hi)
     return (lo, hi) if hi > lo else (0, 0)

@@ -205,3 +205,17 @@ def test_lease_asks_for_a_barrier_only_when_none_was_queued_since_the_last_read(
     assert again.needs_barrier()              # the pool remembers when the allocation was last read
     peers.barrier()
     assert not again.needs_barrier()
+
+
+def test_variable_size_batches_are_balanced_by_tokens():
+    sizes = [(104, 96), (112, 128), (112, 88), (88, 88), (120, 88), (64, 88), (72, 128), (96, 64), (72, 72), (72, 80),
+             (112, 104), (64, 128), (88, 88), (120, 64), (88, 128), (120, 88)]
+    total = sum(h * w for h, w in sizes)
+    for world in (1, 2, 4, 8):
+        parts = sharding.balance_by_tokens(sizes, world)
+        assert sorted(i for p in parts for i in p) == list(range(len(sizes)))
+        loads = [sum(sizes[i][0] * sizes[i][1] for i in p) for p in parts]
+        assert max(loads) <= 1.1 * total / world + max(h * w for h, w in sizes) * (world > 4)
+        by_count = [sum(h * w for h, w in sizes[r::world]) for r in range(world)]
+        assert max(loads) <= max(by_count)
+    assert sharding.balance_by_tokens([5, 1, 1, 1, 1, 1], 2) == [[0], [1, 2, 3, 4, 5]]
