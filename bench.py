@@ -308,9 +308,11 @@ def run_ours(args, w, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    last_stats = {}
+
     def timed(step_fn, steps, trace=False):
         """Mean device milliseconds per step: CUDA events around every step, L2 flushed before each, barrier +
-        synchronize on both sides, maximum over the ranks."""
+        synchronize on both sides, maximum over the ranks.  Median and minimum of the steps go to `last_stats`."""
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
         barrier()
         if trace:
@@ -324,12 +326,15 @@ def run_ours(args, w, rank, world, local_rank):
         barrier()
         if trace:
             _lib.trace_enable(False)
-        ms = sum(a.elapsed_time(b) for a, b in evs)
+        each = sorted(a.elapsed_time(b) for a, b in evs)
+        ms = sum(each)
+        stats = [ms, each[len(each) // 2], each[0]]
         if world > 1:
-            t = torch.tensor([ms], device=dev)
+            t = torch.tensor(stats, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / steps
+            stats = [float(x) for x in t.tolist()]
+        last_stats.update(median=stats[1], min=stats[2])      # of the steps of this call, max over the ranks
+        return stats[0] / steps
 
     # ---- the workload: the named batch sharded over the ranks (strong scaling; at one GPU the whole batch)
     B = w["shape"][0]
@@ -355,6 +360,7 @@ def run_ours(args, w, rank, world, local_rank):
     for _ in range(3):
         main.step()
     ms_plain = timed(main.step, args.steps)                        # the headline: same launches, replayed
+    plain_stats = dict(last_stats)
 
     if args.short:
         if rank == 0:
@@ -449,6 +455,7 @@ def run_ours(args, w, rank, world, local_rank):
                    "l2": "256 MiB buffer written between timed iterations; separate inputs per variant",
                    "kernel_family": path, "flops_model": "fwd 4*B*H*N*K_vol*D, bwd 2.5x fwd",
                    "launch": "CUDA graph replay of the step's launches" if graphed else "eager launches",
+                   "ms_per_step_median": plain_stats.get("median"), "ms_per_step_min": plain_stats.get("min"),
                    "ms_per_step_eager": ms_eager, "ms_per_step_eager_traced": ms_trace,
                    "ms_per_call_fwd_bwd": ms_plain / nvar,
                    "tuned_plans": tuned},
