@@ -10,7 +10,9 @@
 // forward chunk, a backward chunk (S, dP, then the two accumulating products), an N = 256 product as the
 // reference point, and the P V-like product on two alternating accumulators.  Grids of 1, 148 and 296 CTAs
 // (one and two CTAs per SM) show whether the streams of two CTAs of an SM slow each other down.
-// Prints cycles per instruction at issue and at completion.
+// Prints cycles per instruction at issue and at completion; the last three patterns commit and wait after every
+// group of instructions and print cycles per round trip; the three after them issue whole forward chunks with two,
+// three or no commits that nobody waits on and print cycles per chunk.
 #include <cstdio>
 #include <cstdlib>
 #include <cuda.h>
@@ -24,6 +26,7 @@ __global__ void __launch_bounds__(128) k_bench(Args a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t bar_s;
+  __shared__ uint64_t bar_x[3];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -31,7 +34,7 @@ __global__ void __launch_bounds__(128) k_bench(Args a) {
   for (int i = tid; i < 65536 / 16; i += 128) reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   const uint32_t bar = smem_u32(&bar_s);
-  if (tid == 0) { mbar_init(bar, 1); abort_flag = 0; mbar_fence_init(); }
+  if (tid == 0) { mbar_init(bar, 1); for (int i = 0; i < 3; ++i) mbar_init(smem_u32(&bar_x[i]), 1); abort_flag = 0; mbar_fence_init(); }
   __syncthreads();
   if (warp == 0) { tmem_alloc(smem_u32(&tmem_slot), 256); tmem_relinquish(); }
   tc_fence_before(); __syncthreads(); tc_fence_after();
@@ -80,6 +83,37 @@ __global__ void __launch_bounds__(128) k_bench(Args a) {
         }
       }
     }
+    if (a.pattern >= 9) {
+      // a forward chunk with its commits (nobody waits on them): 9: one commit after the SS products and one after
+      // the TS products; 10: a second commit behind the TS products; 11: no commits at all (= pattern 2)
+      const uint32_t bar2 = smem_u32(&bar_x[0]), bar3 = smem_u32(&bar_x[1]), bar4 = smem_u32(&bar_x[2]);
+      for (int r = 0; r < a.reps; ++r) {
+        for (int ks = 0; ks < ksteps; ++ks) { mma_ss(tmem, kk_desc0 + a_lo + 2 * ks, kk_desc0 + b_lo + 2 * ks, idesc_s, ks > 0); ++n_mma; }
+        if (a.pattern != 11) mma_commit(bar2);
+        uint64_t bd = mn_desc0 + b_lo;
+        for (int kk = 0; kk < n_kblk; ++kk) { mma_ts(tmem + 128, tmem + kk * 8, bd, idesc_a, 1); bd += RB; ++n_mma; }
+        if (a.pattern != 11) mma_commit(bar3);
+        if (a.pattern == 10) mma_commit(bar4);
+      }
+      n_mma = a.reps;      // reported per chunk
+    } else if (a.pattern >= 6) {
+      // round trips: a group of instructions, commit, wait for the barrier - the hand-over a chunk of the fused
+      // kernels pays twice (6: one SS product; 7: the ksteps SS products of a chunk; 8: the n_kblk TS products)
+      for (int r = 0; r < a.reps; ++r) {
+        if (a.pattern == 6) { mma_ss(tmem, kk_desc0 + a_lo, kk_desc0 + b_lo, idesc_s, 0); ++n_mma; }
+        if (a.pattern == 7)
+          for (int ks = 0; ks < ksteps; ++ks) { mma_ss(tmem, kk_desc0 + a_lo + 2 * ks, kk_desc0 + b_lo + 2 * ks, idesc_s, ks > 0); ++n_mma; }
+        if (a.pattern == 8) {
+          uint64_t bd = mn_desc0 + b_lo;
+          for (int kk = 0; kk < n_kblk; ++kk) { mma_ts(tmem + 128, tmem + kk * 8, bd, idesc_a, 1); bd += RB; ++n_mma; }
+        }
+        mma_commit(bar);
+        bool got = false;
+        for (uint32_t i = 0; i < 4000 && !got; ++i) got = mbar_try_wait(bar, parity);
+        parity ^= 1;
+      }
+      n_mma = a.reps;      // reported per round trip
+    }
     long long t_issue = clock64();
     mma_commit(bar);
     bool done = false;
@@ -94,11 +128,13 @@ __global__ void __launch_bounds__(128) k_bench(Args a) {
 int main() {
   long long* out; cudaMalloc(&out, 64);
   cudaFuncSetAttribute(k_bench, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-  const char* names[] = {"SS QK-like", "TS PV-like", "QK+PV chunk", "SS N=256", "TS alt-acc", "bwd chunk"};
+  const char* names[] = {"SS QK-like", "TS PV-like", "QK+PV chunk", "SS N=256", "TS alt-acc", "bwd chunk",
+                         "1 SS + commit + wait", "chunk SS + commit + wait", "chunk TS + commit + wait",
+                         "chunk, 2 commits, no wait", "chunk, 3 commits, no wait", "chunk, no commits"};
   struct Cfg { int RB, layout, npad, D; } cfgs[] = {{64, 4, 96, 32}, {128, 2, 64, 64}, {128, 2, 128, 64}, {64, 4, 48, 32}, {32, 6, 96, 32}, {32, 6, 48, 32}, {32, 0, 96, 32}};
   for (auto c : cfgs)
     for (int grid : {1, 148, 296})
-      for (int pat = 0; pat < 6; ++pat) {
+      for (int pat = 0; pat < 12; ++pat) {
         if (pat == 5 && (c.D != 32 || 2 * c.npad > 192)) continue;
         if (pat == 3 && c.npad != 96 && c.npad != 64) continue;
         Args a{pat, 64, c.RB, c.layout, c.npad, c.D, out};
