@@ -220,7 +220,7 @@ def run_reference(args, w, rank, world):
     line = {
         "impl": "reference", "metric": "na_fwd_bwd_effective_tflops", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": w["label"], "note": "CPU restatement of the reference's pure backend (torch CPU ops)"},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
@@ -449,7 +449,7 @@ def run_ours(args, w, rank, world, local_rank):
     line = {
         "metric": "na_fwd_bwd_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_plain, "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
         "config": {"workload": w["label"], "calls_per_step": nvar, "per_gpu_batch": hi - lo,
                    "global_batch": B, "parallelism": f"batch of {B} sharded over {world} rank(s), no collective",
                    "l2": "256 MiB buffer written between timed iterations; separate inputs per variant",
