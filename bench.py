@@ -380,7 +380,7 @@ def run_ours(args, w, rank, world, local_rank):
     d2h = sum(t.numel() * t.element_size() for ho in host_out for t in ho)
     from natten_mlx_b200.host import HostPipeline
     pipes = [HostPipeline(w_loc["shape"], host_in[0][0].dtype, dev, w["kernel"], dilation=dil, is_causal=w["causal"],
-                          heads_kv=w["heads_kv"], slabs=8) for dil in w["dilations"]]
+                          heads_kv=w["heads_kv"], slabs=4) for dil in w["dilations"]]
 
     def step_e2e():
         for hi_, ho, pipe in zip(host_in, host_out, pipes):     # the variants share the streams and keep streaming
