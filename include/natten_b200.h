@@ -306,6 +306,25 @@ int natten_b200_peer_barrier(const uint64_t* flag_blocks, int32_t world, int32_t
                              uint32_t timeout_ms, void* stream);
 
 /*
+ * The fused backward of one slab of a volume sharded along its leading axis, with the halo reduction of dK / dV
+ * folded into the dK/dV kernel: gradients of the first planes_below and the last planes_above planes of the K/V
+ * slab - planes another rank owns - are not written to dk / dv but stored by the kernel's epilogue, tile by tile,
+ * straight into dk_below / dv_below and dk_above / dv_above, laid out [batch, planes, rest of the K/V layout]
+ * (normally the owner's staging area in peer-mapped memory: plain 16-byte stores cross NVLink while the kernel
+ * computes; natten_b200_peer_barrier then tells the owner that they have arrived).  Tensor-core kernels only
+ * (bf16 / fp16 shapes they take; NATTEN_B200_EINVAL otherwise), no extra tokens, no per-sample extents.  The
+ * other arguments are those of natten_b200_fused_backward.  No counterpart in the reference (single device).
+ */
+typedef struct natten_b200_halo_out {
+  int32_t planes_below, planes_above;
+  void *dk_below, *dv_below, *dk_above, *dv_above;
+} natten_b200_halo_out;
+int natten_b200_fused_backward_halo(const natten_b200_geom* g, const void* q, const void* k,
+                                    const void* v, const void* out, const float* lse, const void* dout,
+                                    const float* dlse, void* dq, void* dk, void* dv, void* scratch,
+                                    size_t scratch_bytes, const natten_b200_halo_out* halo, void* stream);
+
+/*
  * Merge two attention results over the same queries:
  * out = o0 - sigmoid(l1 - l0) * (o0 - o1), lse = l0 - logsigmoid(l0 - l1).
  * rows = number of (query, head) rows, o* are [rows, head_dim] in dtype,

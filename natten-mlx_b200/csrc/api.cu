@@ -391,6 +391,41 @@ int natten_b200_fused_backward(const natten_b200_geom* gi, const void* q, const 
   return run_fused_backward_simt(g, gi->dtype, a, (cudaStream_t)stream);
 }
 
+int natten_b200_fused_backward_halo(const natten_b200_geom* gi, const void* q, const void* k,
+                                    const void* v, const void* out, const float* lse, const void* dout,
+                                    const float* dlse, void* dq, void* dk, void* dv, void* scratch,
+                                    size_t scratch_bytes, const natten_b200_halo_out* halo, void* stream) {
+  Geo g;
+  if (int rc = make_geo(gi, &g)) return rc;
+  if (halo == nullptr) return set_error(NATTEN_B200_EINVAL, "fused_backward_halo: halo is null");
+  if (any_null({q, k, v, out, lse, dout, dq, dk, dv, scratch}))
+    return set_error(NATTEN_B200_EINVAL, "fused_backward_halo: null tensor");
+  if (any_misaligned({q, k, v, out, dout, dq, dk, dv, scratch, halo->dk_below, halo->dv_below, halo->dk_above, halo->dv_above}))
+    return reject_misaligned("fused_backward_halo");
+  if (g.n_extra != 0 || g.extents != nullptr)
+    return set_error(NATTEN_B200_EINVAL, "fused_backward_halo: extra tokens and per-sample extents are not supported");
+  if (g.rank != 3 || halo->planes_below < 0 || halo->planes_above < 0 || halo->planes_below + halo->planes_above > g.ke[0])
+    return set_error(NATTEN_B200_EINVAL, "fused_backward_halo: needs a 3-D slab whose K/V planes include the halo planes");
+  if ((halo->planes_below > 0 && any_null({halo->dk_below, halo->dv_below})) ||
+      (halo->planes_above > 0 && any_null({halo->dk_above, halo->dv_above})))
+    return set_error(NATTEN_B200_EINVAL, "fused_backward_halo: a halo destination is null");
+  if (scratch_bytes < natten_b200_fused_backward_scratch_bytes(gi))
+    return set_error(NATTEN_B200_ERESOURCE, "fused_backward_halo: scratch has %zu bytes, needs %zu", scratch_bytes,
+                     natten_b200_fused_backward_scratch_bytes(gi));
+  if (gi->path == NATTEN_B200_PATH_SIMT || !sm100_backward_supported(g, gi->dtype))
+    return set_error(NATTEN_B200_EINVAL, "fused_backward_halo: needs the tensor-core kernels: %s",
+                     sm100_unsupported_reason(g, gi->dtype));
+  FusedArgs a{};
+  a.q = q; a.k = k; a.v = v;
+  a.out = const_cast<void*>(out); a.lse = const_cast<float*>(lse); a.dout = dout; a.dlse = dlse;
+  a.dq = dq; a.dk = dk; a.dv = dv;
+  a.scratch = scratch; a.scratch_bytes = scratch_bytes;
+  a.halo_below = halo->planes_below; a.halo_above = halo->planes_above;
+  a.dk_below = halo->dk_below; a.dv_below = halo->dv_below; a.dk_above = halo->dk_above; a.dv_above = halo->dv_above;
+  set_last_path("tcgen05");
+  return run_fused_backward_sm100(g, gi->dtype, a, (cudaStream_t)stream);
+}
+
 int natten_b200_kernel_status(void) { return sm100_read_status(); }
 
 #ifdef NB_SM100_PROFILE

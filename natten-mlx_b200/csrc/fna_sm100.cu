@@ -86,6 +86,10 @@ struct FwdParams {
   const float* lse_in;                // saved log-sum-exp [rows of out] (natural log)
   const float* delta;                 // rowsum(dO * O) - dLSE [rows of out]
   void* out2;                         // dV (mode 2)
+  // mode 2 on a slab: dK / dV rows of the first halo_lo and the last halo_hi planes of the K/V slab go to these
+  // tensors ([batch, planes, rest of the layout]; memory of a neighbouring GPU) instead of out / out2
+  int halo_lo, halo_hi;
+  void *out_lo, *out2_lo, *out_hi, *out2_hi;
   int tiles[3];
   long long n_work;
   float scale_log2;

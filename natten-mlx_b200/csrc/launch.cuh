@@ -52,6 +52,10 @@ struct FusedArgs {
   void *dq, *dk, *dv, *dk_extra, *dv_extra;
   void* scratch;
   size_t scratch_bytes;
+  // dK/dV of the leading / trailing planes of a K/V slab written elsewhere (another GPU's staging area): plane
+  // counts and destinations laid out [batch, planes, rest of the K/V layout]; zeros when unused
+  int halo_below = 0, halo_above = 0;
+  void *dk_below = nullptr, *dv_below = nullptr, *dk_above = nullptr, *dv_above = nullptr;
 };
 
 int run_fused_forward_simt(const Geo& g, int dtype, const FusedArgs& a, cudaStream_t s);

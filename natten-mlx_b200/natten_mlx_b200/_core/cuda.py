@@ -11,6 +11,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
+import ctypes
+
 import torch
 
 from .. import _lib
@@ -235,8 +237,12 @@ def fused_forward(q, k, v, ks, st, dl, ca, scale, *, k_extra=None, v_extra=None,
 
 
 def fused_backward(q, k, v, out, lse, grad_out, grad_lse, ks, st, dl, ca, scale, *, k_extra=None,
-                   v_extra=None, sizes=None, slab: Optional[Slab] = None, path=None, host_sizes=None):
-    """Returns (dq, dk, dv, dk_extra, dv_extra); the last two are None without extra tokens."""
+                   v_extra=None, sizes=None, slab: Optional[Slab] = None, path=None, host_sizes=None, halo_out=None):
+    """Returns (dq, dk, dv, dk_extra, dv_extra); the last two are None without extra tokens.
+
+    ``halo_out`` = (planes_below, planes_above, dk_below, dv_below, dk_above, dv_above) with raw addresses sends
+    the gradients of a slab's halo planes there from inside the dK/dV kernel (tensor-core kernels only; see
+    ``natten_b200_fused_backward_halo``); those planes of the returned dk / dv are then left unwritten."""
     rank = q.dim() - 3
     q, k, v, k_extra, v_extra, out, grad_out = _prep(q, k, v, k_extra, v_extra, out, grad_out)
     n_extra = 0 if k_extra is None else k_extra.shape[1]
@@ -254,6 +260,12 @@ def fused_backward(q, k, v, out, lse, grad_out, grad_lse, ks, st, dl, ca, scale,
     nbytes = int(lib.natten_b200_fused_backward_scratch_bytes(g))
     scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
+        if halo_out is not None:
+            halo = _lib.HaloOut(int(halo_out[0]), int(halo_out[1]), *[int(x) if x else None for x in halo_out[2:6]])
+            _lib.check(lib.natten_b200_fused_backward_halo(
+                g, _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(grad_out), _ptr(grad_lse), _ptr(dq), _ptr(dk),
+                _ptr(dv), _ptr(scratch), nbytes, ctypes.byref(halo), _stream(q)))
+            return dq, dk, dv, dke, dve
         _lib.check(lib.natten_b200_fused_backward(
             g, _ptr(q), _ptr(k), _ptr(v), _ptr(k_extra), _ptr(v_extra), _ptr(out), _ptr(lse), _ptr(grad_out),
             _ptr(grad_lse), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dke), _ptr(dve), _ptr(scratch), nbytes, _stream(q)))

@@ -73,6 +73,7 @@ SYMBOLS = {
     "natten_b200_fused_backward": (ctypes.c_int, [_G] + [_P] * 15 + [ctypes.c_size_t, _P]),
     "natten_b200_static_scratch_capacity": (ctypes.c_size_t, []),
     "natten_b200_fused_backward_static_scratch": (ctypes.c_int, [_G] + [_P] * 15),
+    "natten_b200_fused_backward_halo": (ctypes.c_int, [_G] + [_P] * 11 + [ctypes.c_size_t, _P, _P]),
     "natten_b200_kernel_status": (ctypes.c_int, []),
     "natten_b200_peer_copy2d": (ctypes.c_int, [_P, ctypes.c_size_t, _P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, _P]),
     "natten_b200_peer_barrier": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint32, _P]),
@@ -81,6 +82,13 @@ SYMBOLS = {
     "natten_b200_merge_forward": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32] + [_P] * 7),
     "natten_b200_merge_backward": (ctypes.c_int, [ctypes.c_int32, ctypes.c_int64, ctypes.c_int32] + [_P] * 11),
 }
+
+class HaloOut(ctypes.Structure):
+    """Mirrors natten_b200_halo_out: where the dK / dV of a slab's halo planes go."""
+    _fields_ = [("planes_below", ctypes.c_int32), ("planes_above", ctypes.c_int32),
+                ("dk_below", ctypes.c_void_p), ("dv_below", ctypes.c_void_p),
+                ("dk_above", ctypes.c_void_p), ("dv_above", ctypes.c_void_p)]
+
 
 _lib: Optional[ctypes.CDLL] = None
 

@@ -480,51 +480,92 @@ def exchange_halos_peer(locals_: Sequence[torch.Tensor], plans: Sequence[SlabPla
     return bufs, lease
 
 
+class _PeerReduce:
+    """The halo reduction of dK / dV over peer memory, in its two halves: ``open`` reserves the staging areas (and
+    queues the barrier that protects them, if one is due) and knows where this rank's partial sums go;
+    ``close`` queues the arrival barrier and adds what the neighbours delivered into the owned planes.  Between
+    the two the partial sums are delivered either by the copy kernel (``push``) or by the dK/dV kernel itself
+    (``halo_out``: its epilogue stores the halo planes' gradients straight into the owner's staging area)."""
+
+    def __init__(self, like: Sequence[torch.Tensor], plans, rank, group, axis=1):
+        self.t = peer_transport(group)
+        self.plans, self.rank, self.axis = plans, rank, axis
+        self.me = plans[rank]
+        self.rows = 1
+        for x in like[0].shape[:axis]:
+            self.rows *= x
+        self.pb = [_plane_bytes(x, axis) for x in like]
+        self.where, span = staging_layout(plans)
+        self.offs, total = [], 0
+        for b in self.pb:
+            self.offs.append(total)
+            total += _align(self.rows * span * b)
+        self.transfers = halo_transfers(plans)
+        self.lease = None
+        if total:
+            self.lease = self.t.acquire(total)
+            if self.lease.needs_barrier():
+                self.t.barrier()                  # the owners have finished with what the last call left there
+
+    def target(self, i: int, owner: int) -> int:
+        """Address, in this process, of the area where ``owner`` keeps this rank's partial sums of tensor ``i``."""
+        return self.lease.ptrs[owner] + self.offs[i] + self.where[(owner, self.rank)] * self.rows * self.pb[i]
+
+    def halo_out(self):
+        """(planes_below, planes_above, dk_below, dv_below, dk_above, dv_above) for the dK/dV kernel, or None when
+        the halo planes of this rank do not belong to its two direct neighbours alone."""
+        me, below, above = self.me, self.me.q_lo - self.me.kv_lo, self.me.kv_hi - self.me.q_hi
+        mine = [(o, lo, hi) for o, b, lo, hi in self.transfers if b == self.rank]
+        want = ([(self.rank - 1, me.kv_lo, me.q_lo)] if below else []) + ([(self.rank + 1, me.q_hi, me.kv_hi)] if above else [])
+        if sorted(mine) != sorted(want) or len(self.pb) != 2:
+            return None
+        lo = [self.target(i, self.rank - 1) if below else 0 for i in range(2)]
+        hi = [self.target(i, self.rank + 1) if above else 0 for i in range(2)]
+        return (below, above, lo[0], lo[1], hi[0], hi[1])
+
+    def push(self, grad_bufs):
+        """Deliver the partial sums held in the halo planes of ``grad_bufs`` with the copy kernel."""
+        me = self.me
+        for i, g in enumerate(grad_bufs):
+            for owner, borrower, lo, hi in self.transfers:
+                if borrower != self.rank:
+                    continue
+                # the owner's area holds rows of (hi - lo) planes for this borrower, densely: pitch = width
+                self.t.copy2d(self.target(i, owner), (hi - lo) * self.pb[i], g.data_ptr() + (lo - me.kv_lo) * self.pb[i],
+                              (me.kv_hi - me.kv_lo) * self.pb[i], (hi - lo) * self.pb[i], self.rows)
+
+    def close(self, grad_bufs) -> List[torch.Tensor]:
+        me, axis = self.me, self.axis
+        owns = [g.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo) for g in grad_bufs]
+        if self.lease is None:
+            return owns
+        self.t.barrier()                          # the partials for this rank's planes have arrived
+        for i, own in enumerate(owns):
+            for owner, borrower, lo, hi in self.transfers:
+                if owner != self.rank:
+                    continue
+                shape = list(own.shape)
+                shape[axis] = hi - lo
+                n = 1
+                for x in shape:
+                    n *= x
+                start = self.offs[i] + self.where[(owner, borrower)] * self.rows * self.pb[i]
+                piece = self.lease.tensor[start: start + n * own.element_size()].view(own.dtype).view(shape)
+                own.narrow(axis, lo - me.q_lo, hi - lo).add_(piece)
+        self.lease.mark_read()
+        self.lease.release()
+        self.lease = None
+        return owns
+
+
 def reduce_halo_grads_peer(grad_bufs: Sequence[torch.Tensor], plans: Sequence[SlabPlan], rank: int, group=None,
                            axis: int = 1) -> List[torch.Tensor]:
-    """``reduce_halo_grads_many`` over peer memory: partial sums are written into the owner's staging area, the
-    owner adds them into its planes."""
-    t = peer_transport(group)
-    me = plans[rank]
-    rows = 1
-    for x in grad_bufs[0].shape[:axis]:
-        rows *= x
-    pb = [_plane_bytes(x, axis) for x in grad_bufs]
-    where, span = staging_layout(plans)
-    offs, total = [], 0
-    for b in pb:
-        offs.append(total)
-        total += _align(rows * span * b)
-    owns = [g.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo) for g in grad_bufs]
-    if total == 0:
-        return owns
-    lease = t.acquire(total)
-    transfers = halo_transfers(plans)
-    if lease.needs_barrier():
-        t.barrier()                               # the owners have finished with what the last call left there
-    for i, g in enumerate(grad_bufs):
-        for owner, borrower, lo, hi in transfers:
-            if borrower != rank:
-                continue
-            # the owner's area holds rows of (hi - lo) planes for this borrower, densely: pitch = width
-            t.copy2d(lease.ptrs[owner] + offs[i] + where[(owner, borrower)] * rows * pb[i], (hi - lo) * pb[i],
-                     g.data_ptr() + (lo - me.kv_lo) * pb[i], (me.kv_hi - me.kv_lo) * pb[i], (hi - lo) * pb[i], rows)
-    t.barrier()                                   # the partials for this rank's planes have arrived
-    for i, own in enumerate(owns):
-        for owner, borrower, lo, hi in transfers:
-            if owner != rank:
-                continue
-            shape = list(own.shape)
-            shape[axis] = hi - lo
-            n = 1
-            for x in shape:
-                n *= x
-            start = offs[i] + where[(owner, borrower)] * rows * pb[i]
-            piece = lease.tensor[start: start + n * own.element_size()].view(own.dtype).view(shape)
-            own.narrow(axis, lo - me.q_lo, hi - lo).add_(piece)
-    lease.mark_read()
-    lease.release()
-    return owns
+    """``reduce_halo_grads_many`` over peer memory: partial sums are written into the owner's staging area by the
+    copy kernel, the owner adds them into its planes."""
+    red = _PeerReduce(grad_bufs, plans, rank, group, axis)
+    if red.lease is not None:
+        red.push(grad_bufs)
+    return red.close(grad_bufs)
 
 
 def _global_rank(group_rank: int, group) -> int:
@@ -547,6 +588,17 @@ def fused_slab_forward_backward(q, k_buf, v_buf, grad_out, plan: SlabPlan, exten
     out, lse = _cuda.fused_forward(q, k_buf, v_buf, ks, one, dl, ca, scale, slab=slab)
     dq, dk, dv, _, _ = _cuda.fused_backward(q, k_buf, v_buf, out, lse, grad_out, None, ks, one, dl, ca, scale, slab=slab)
     return out, lse, dq, dk, dv
+
+
+def _tensor_core_slab(q, k_buf, ks, one, dl, ca, scale, slab) -> bool:
+    """Whether the fused backward of this slab runs on the tensor-core kernels (which can deliver halo gradients)."""
+    if q.dtype not in (torch.float16, torch.bfloat16) or _cuda.get_fused_path() == "simt":
+        return False
+    geom = _cuda._geom(q, k_buf, q.dim() - 3, ks, one, dl, ca, _cuda._scale(scale, q.shape[-1]), slab=slab)
+    try:
+        return "unsupported" not in _lib.describe_plan(geom)
+    except ValueError:
+        return False
 
 
 class _ShardedNA(torch.autograd.Function):
@@ -577,15 +629,24 @@ class _ShardedNA(torch.autograd.Function):
         extent, ks, dl, ca, scale, plans, rank, group, slab, one, peer = ctx.args
         if grad_out is None:
             grad_out = torch.zeros_like(out)
+        red = halo = None
+        if peer:
+            # staging areas first: with the tensor-core kernels the dK/dV kernel itself delivers the halo planes'
+            # partial sums into the owners' staging areas while it computes
+            red = _PeerReduce([k_buf, v_buf], plans, rank, group)
+            if red.lease is not None and _tensor_core_slab(q, k_buf, ks, one, dl, ca, scale, slab):
+                halo = red.halo_out()
         dq, dk, dv, _, _ = _cuda.fused_backward(q, k_buf, v_buf, out, lse, grad_out, grad_lse, ks, one, dl, ca,
-                                                scale, slab=slab)
+                                                scale, slab=slab, halo_out=halo)
         if ctx.lease is not None:
             ctx.lease.mark_read()
             if not ctx.lease.persistent:
                 ctx.lease.release()
             ctx.lease = None
         if peer:
-            dk, dv = reduce_halo_grads_peer([dk, dv], plans, rank, group)
+            if halo is None and red.lease is not None:
+                red.push([dk, dv])
+            dk, dv = red.close([dk, dv])
         else:
             dk, dv = reduce_halo_grads_many([dk, dv], plans, rank, group)
         return (dq, dk, dv) + (None,) * 9

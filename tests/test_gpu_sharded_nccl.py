@@ -67,6 +67,31 @@ def _worker(rank, world, port, causal, results):
                 ok.append(torch.allclose(a, b.grad[:, lo:hi], atol=1e-4, rtol=1e-4))
         kv_lease.release()
         ok.append(_lib.kernel_status() == 0)          # no barrier gave up on its wait
+        # bf16 on the tensor-core kernels: the dK/dV kernel itself delivers the halo planes' gradients into the
+        # neighbours' staging areas (no copy kernel in the backward)
+        bf = torch.bfloat16
+        gen = torch.Generator().manual_seed(33)
+        full16 = [torch.randn((2, T, 10, 16, 2, 32), generator=gen).to(bf) for _ in range(4)]
+        ks16, dl16 = (3, 3, 5), (1, 1, 2)
+        qf, kf, vf = (t.to(dev).requires_grad_(True) for t in full16[:3])
+        ref16 = nb.na3d(qf, kf, vf, kernel_size=ks16, dilation=dl16, is_causal=ca)
+        ref16.backward(full16[3].to(dev))
+        tc = _lib.last_path() == "tcgen05"
+        rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        for _ in range(2):
+            q, k, v = (t[:, lo:hi].to(dev).requires_grad_(True) for t in full16[:3])
+            out = sharding.na_sharded(q, k, v, T, ks16, dl16, ca, transport="peer")
+            _lib.trace_report()
+            _lib.trace_enable(True)
+            out.backward(full16[3][:, lo:hi].to(dev))
+            torch.cuda.synchronize()
+            _lib.trace_enable(False)
+            names = set(_lib.trace_report())
+            ok.append(tc and "fna_bwd_dkv_sm100" in names and "peer_copy2d" not in names and "peer_barrier" in names)
+            ok.append(rel(out, ref16[:, lo:hi]) < 2e-2)
+            for a, b in ((q, qf), (k, kf), (v, vf)):
+                ok.append(rel(a.grad, b.grad[:, lo:hi]) < 2e-2)
+        ok.append(_lib.kernel_status() == 0)
         with torch.no_grad():                          # nothing saved: the buffers go straight back to the pool
             q, k, v = (t[:, lo:hi].to(dev) for t in full[:3])
             ok.append(torch.allclose(sharding.na_sharded(q, k, v, T, ks, dl, ca, transport="peer"), ref[:, lo:hi],
@@ -86,4 +111,4 @@ def test_na_sharded_matches_unsharded_over_nccl(causal):
     mp.spawn(_worker, args=(world, _free_port(), causal, results), nprocs=world, join=True)
     assert len(results) == world
     for r in range(world):
-        assert all(results[r]) and len(results[r]) == 23, (r, results[r])
+        assert all(results[r]) and len(results[r]) == 34, (r, results[r])
