@@ -182,6 +182,60 @@ def test_leading_axis_slabs_on_the_tensor_core_kernels(shape, ks, dl, ca, world)
     assert _rel(dv_full, g_ref[2]) < 2e-2
 
 
+@pytest.mark.parametrize("shape,ks,dl,ca,world", [
+    ((2, 12, 9, 10, 2, 32), (3, 3, 5), (1, 1, 1), (True, False, False), 2),
+    ((2, 16, 12, 16, 4, 64), (5, 7, 3), (1, 1, 2), (False, False, False), 3),
+])
+def test_dkdv_kernel_delivers_the_gradients_of_halo_planes_elsewhere(shape, ks, dl, ca, world):
+    """``halo_out``: the dK/dV kernel stores the gradients of a slab's leading / trailing halo planes into other
+    tensors ([batch, planes, ...]; on several GPUs the neighbours' staging areas) and leaves those planes of
+    dk / dv alone; everything equals the plain slab backward bit for bit."""
+    from natten_mlx_b200 import sharding
+    dt = torch.bfloat16
+    q, k, v, cot = (_rand(shape, 300 + i, dt).to(DEV) for i in range(4))
+    one = (1, 1, 1)
+    T = shape[1]
+    seen = 0
+    for r in range(world):
+        plan = sharding.slab_plan(T, world, r, ks[0], dl[0], ca[0])
+        below, above = plan.q_lo - plan.kv_lo, plan.kv_hi - plan.q_hi
+        slab = sharding._slab(plan, shape[1:4])
+        qs, ks_, vs, cs = (t[:, a:b].contiguous() for t, (a, b) in
+                           ((q, (plan.q_lo, plan.q_hi)), (k, (plan.kv_lo, plan.kv_hi)), (v, (plan.kv_lo, plan.kv_hi)),
+                            (cot, (plan.q_lo, plan.q_hi))))
+        o, lse = backend.fused_forward(qs, ks_, vs, ks, one, dl, ca, None, slab=slab, path="tcgen05")
+        dq0, dk0, dv0, _, _ = backend.fused_backward(qs, ks_, vs, o, lse, cs, None, ks, one, dl, ca, None, slab=slab,
+                                                     path="tcgen05")
+        if below + above == 0:
+            continue
+        seen += 1
+        mk = lambda n: torch.full((shape[0], max(n, 1)) + tuple(ks_.shape[2:]), 7.0, dtype=dt, device=DEV)
+        kb, vb, ka, va = mk(below), mk(below), mk(above), mk(above)
+        halo = (below, above, kb.data_ptr() if below else 0, vb.data_ptr() if below else 0,
+                ka.data_ptr() if above else 0, va.data_ptr() if above else 0)
+        dq1, dk1, dv1, _, _ = backend.fused_backward(qs, ks_, vs, o, lse, cs, None, ks, one, dl, ca, None, slab=slab,
+                                                     path="tcgen05", halo_out=halo)
+        torch.cuda.synchronize()
+        assert _lib.kernel_status() == 0
+        n = ks_.shape[1]
+        assert torch.equal(dq1, dq0)
+        assert torch.equal(dk1[:, below:n - above], dk0[:, below:n - above])
+        assert torch.equal(dv1[:, below:n - above], dv0[:, below:n - above])
+        if below:
+            assert torch.equal(kb, dk0[:, :below]) and torch.equal(vb, dv0[:, :below])
+        if above:
+            assert torch.equal(ka, dk0[:, n - above:]) and torch.equal(va, dv0[:, n - above:])
+    assert seen >= world - 1
+    with pytest.raises(ValueError, match="tensor-core"):        # the float32 kernels have no such output
+        f = lambda t: t.float()
+        plan = sharding.slab_plan(T, world, 1, ks[0], dl[0], ca[0])
+        slab = sharding._slab(plan, shape[1:4])
+        qs, ks_, vs = f(q[:, plan.q_lo:plan.q_hi]), f(k[:, plan.kv_lo:plan.kv_hi]), f(v[:, plan.kv_lo:plan.kv_hi])
+        o, lse = backend.fused_forward(qs, ks_, vs, ks, one, dl, ca, None, slab=slab)
+        backend.fused_backward(qs, ks_, vs, o, lse, f(cot[:, plan.q_lo:plan.q_hi]), None, ks, one, dl, ca, None, slab=slab,
+                               halo_out=(1, 0, o.data_ptr(), o.data_ptr(), 0, 0))
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs in one process")
 def test_two_devices_in_one_process():
     """The opt-in to large dynamic shared memory belongs to a device's context: the tensor-core kernels must launch
