@@ -302,6 +302,10 @@ int natten_b200_fused_backward_static_scratch(const natten_b200_geom* g, const v
  */
 int natten_b200_peer_copy2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
                             size_t width_bytes, size_t rows, void* stream);
+/* The same copy through a copy engine (cudaMemcpy2DAsync) instead of a kernel: it occupies no SM, so it can run on a
+ * second stream under a kernel that fills the GPU. */
+int natten_b200_peer_copy2d_dma(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                size_t width_bytes, size_t rows, void* stream);
 int natten_b200_peer_barrier(const uint64_t* flag_blocks, int32_t world, int32_t rank, uint32_t epoch,
                              uint32_t timeout_ms, void* stream);
 

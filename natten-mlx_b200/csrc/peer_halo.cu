@@ -96,6 +96,19 @@ int natten_b200_peer_copy2d(void* dst, size_t dst_pitch, const void* src, size_t
   return check_launch("peer_copy2d");
 }
 
+int natten_b200_peer_copy2d_dma(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                                size_t rows, void* stream) {
+  using namespace nb;
+  if (width_bytes == 0 || rows == 0) return NATTEN_B200_OK;
+  if (dst == nullptr || src == nullptr) return set_error(NATTEN_B200_EINVAL, "peer copy: null pointer");
+  if (rows > 1 && (dst_pitch < width_bytes || src_pitch < width_bytes))
+    return set_error(NATTEN_B200_EINVAL, "peer copy: a pitch is smaller than the width");
+  const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault,
+                                          static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return set_error(NATTEN_B200_ELAUNCH, "peer copy (copy engine): %s", cudaGetErrorString(e));
+  return NATTEN_B200_OK;
+}
+
 int natten_b200_peer_barrier(const uint64_t* flag_blocks, int32_t world, int32_t rank, uint32_t epoch, uint32_t timeout_ms,
                              void* stream) {
   using namespace nb;

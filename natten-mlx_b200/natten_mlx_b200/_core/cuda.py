@@ -217,8 +217,9 @@ def _host_sizes(sizes, host_sizes, batch, rank):
 
 
 def fused_forward(q, k, v, ks, st, dl, ca, scale, *, k_extra=None, v_extra=None, sizes=None,
-                  slab: Optional[Slab] = None, path=None, host_sizes=None):
-    """Returns (out, lse); lse is float32 [B, out..., H_q].  With per-sample ``sizes`` the padding of both is zero."""
+                  slab: Optional[Slab] = None, path=None, host_sizes=None, out=None, lse=None):
+    """Returns (out, lse); lse is float32 [B, out..., H_q].  With per-sample ``sizes`` the padding of both is zero.
+    ``out`` / ``lse`` (both or neither): dense tensors to write into instead of new ones."""
     rank = q.dim() - 3
     q, k, v, k_extra, v_extra = _prep(q, k, v, k_extra, v_extra)
     n_extra = 0 if k_extra is None else k_extra.shape[1]
@@ -228,8 +229,14 @@ def fused_forward(q, k, v, ks, st, dl, ca, scale, *, k_extra=None, v_extra=None,
     outs = _out_shape(q.shape[1:1 + rank], st)
     # variable-size batches: the tensor-core kernels never touch rows outside a sample, so they start from zeros
     alloc = torch.empty if sizes is None else torch.zeros
-    out = alloc((q.shape[0],) + outs + tuple(q.shape[-2:]), dtype=q.dtype, device=q.device)
-    lse = alloc((q.shape[0],) + outs + (q.shape[-2],), dtype=torch.float32, device=q.device)
+    if out is not None:
+        want = (q.shape[0],) + outs + tuple(q.shape[-2:])
+        if (tuple(out.shape) != want or tuple(lse.shape) != want[:-1] or not out.is_contiguous() or not lse.is_contiguous()
+                or out.dtype != q.dtype or lse.dtype != torch.float32 or sizes is not None):
+            raise ValueError("fused_forward: out / lse must be dense tensors of the result's shapes and dtypes")
+    else:
+        out = alloc((q.shape[0],) + outs + tuple(q.shape[-2:]), dtype=q.dtype, device=q.device)
+        lse = alloc((q.shape[0],) + outs + (q.shape[-2],), dtype=torch.float32, device=q.device)
     with torch.cuda.device(q.device):
         _lib.check(_lib.load().natten_b200_fused_forward(g, _ptr(q), _ptr(k), _ptr(v), _ptr(k_extra), _ptr(v_extra),
                                                          _ptr(out), _ptr(lse), _stream(q)))

@@ -76,6 +76,7 @@ SYMBOLS = {
     "natten_b200_fused_backward_halo": (ctypes.c_int, [_G] + [_P] * 11 + [ctypes.c_size_t, _P, _P]),
     "natten_b200_kernel_status": (ctypes.c_int, []),
     "natten_b200_peer_copy2d": (ctypes.c_int, [_P, ctypes.c_size_t, _P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, _P]),
+    "natten_b200_peer_copy2d_dma": (ctypes.c_int, [_P, ctypes.c_size_t, _P, ctypes.c_size_t, ctypes.c_size_t, ctypes.c_size_t, _P]),
     "natten_b200_peer_barrier": (ctypes.c_int, [_P, ctypes.c_int32, ctypes.c_int32, ctypes.c_uint32, ctypes.c_uint32, _P]),
     "natten_b200_describe_plan": (ctypes.c_int, [_G, ctypes.c_char_p, ctypes.c_size_t]),
     "natten_b200_plan_hint": (ctypes.c_int, [_G, ctypes.c_int32, _P, ctypes.c_int32]),

@@ -336,10 +336,19 @@ class PeerTransport:
         handle = self._symm.rendezvous(tensor, self.group)
         return _Lease(self, nbytes, tensor, [int(p) for p in handle.buffer_ptrs])
 
-    def copy2d(self, dst_ptr, dst_pitch, src_ptr, src_pitch, width, rows):
+    def copy2d(self, dst_ptr, dst_pitch, src_ptr, src_pitch, width, rows, dma: bool = False):
+        """Pitched copy on the current stream, by the library's copy kernel or (``dma``) by a copy engine."""
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        _lib.check(_lib.load().natten_b200_peer_copy2d(ctypes.c_void_p(dst_ptr), dst_pitch, ctypes.c_void_p(src_ptr),
-                                                       src_pitch, width, rows, ctypes.c_void_p(stream)))
+        fn = _lib.load().natten_b200_peer_copy2d_dma if dma else _lib.load().natten_b200_peer_copy2d
+        _lib.check(fn(ctypes.c_void_p(dst_ptr), dst_pitch, ctypes.c_void_p(src_ptr), src_pitch, width, rows,
+                      ctypes.c_void_p(stream)))
+
+    @property
+    def side_stream(self):
+        """A high-priority stream for exchanges that run under kernels of the current stream."""
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device, priority=-1)
+        return self._side
 
 
 _transports = {}
@@ -442,12 +451,16 @@ def _registered(locals_):
 
 
 def exchange_halos_peer(locals_: Sequence[torch.Tensor], plans: Sequence[SlabPlan], rank: int, group=None,
-                        axis: int = 1):
+                        axis: int = 1, aside: bool = False):
     """``exchange_halos`` over peer memory: (buffers, lease).  Every rank writes the planes its neighbours need
     straight into their buffers, then a barrier tells everyone that its planes have arrived (a barrier before
     the writes is only queued when none has been queued since the buffers were last read).  The buffers are
     views of the lease's allocation; the caller calls ``lease.mark_read()`` after queueing the kernels that read
-    them and, unless the lease is persistent, ``lease.release()`` when nothing reads them any more."""
+    them and, unless the lease is persistent, ``lease.release()`` when nothing reads them any more.
+
+    ``aside``: the barriers and the writes (then by copy engines) are queued on the transport's side stream, which
+    first waits for the current stream; the result gains a third element, the event after which the halo planes
+    are there.  Kernels that read only owned planes can then run on the current stream in the meantime."""
     t = peer_transport(group)
     me = plans[rank]
     rows = 1
@@ -462,22 +475,40 @@ def exchange_halos_peer(locals_: Sequence[torch.Tensor], plans: Sequence[SlabPla
         pitch = [(me.q_hi - me.q_lo) * b for b in pb]
     else:
         pitch = [(me.kv_hi - me.kv_lo) * b for b in pb]       # the owned planes already sit inside the buffers
-    if lease.needs_barrier():
-        t.barrier()                               # nobody still reads the buffers the writes below go to
     transfers = [x for x in halo_transfers(plans) if x[0] == rank]
-    for i, local in enumerate(locals_):           # what the neighbours wait for goes first
-        for _, borrower, lo, hi in transfers:
-            other = plans[borrower]
-            t.copy2d(lease.ptrs[borrower] + offs[i] + (lo - other.kv_lo) * pb[i], (other.kv_hi - other.kv_lo) * pb[i],
-                     local.data_ptr() + (lo - me.q_lo) * pb[i], pitch[i], (hi - lo) * pb[i], rows)
-    bufs = []
-    for i, local in enumerate(locals_):
-        buf = _buffer_view(lease, offs[i], local.shape, local.dtype, me, axis)
+    bufs = [_buffer_view(lease, offs[i], local.shape, local.dtype, me, axis) for i, local in enumerate(locals_)]
+
+    def own_planes():
         if not lease.persistent:
-            buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo).copy_(local)
-        bufs.append(buf)
-    t.barrier()                                   # the planes others wrote into this rank's buffers have arrived
-    return bufs, lease
+            for buf, local in zip(bufs, locals_):
+                buf.narrow(axis, me.q_lo - me.kv_lo, me.q_hi - me.q_lo).copy_(local)
+
+    def exchange(dma):
+        if lease.needs_barrier():
+            t.barrier()                           # nobody still reads the buffers the writes below go to
+        for i, local in enumerate(locals_):       # what the neighbours wait for goes first
+            for _, borrower, lo, hi in transfers:
+                other = plans[borrower]
+                t.copy2d(lease.ptrs[borrower] + offs[i] + (lo - other.kv_lo) * pb[i], (other.kv_hi - other.kv_lo) * pb[i],
+                         local.data_ptr() + (lo - me.q_lo) * pb[i], pitch[i], (hi - lo) * pb[i], rows, dma=dma)
+
+    if not aside:
+        exchange(False)
+        own_planes()
+        t.barrier()                               # the planes others wrote into this rank's buffers have arrived
+        return bufs, lease
+    main = torch.cuda.current_stream(t.device)
+    side = t.side_stream
+    side.wait_stream(main)                        # the K/V to lend exist; earlier readers of the buffers are done
+    with torch.cuda.stream(side):
+        exchange(True)
+        t.barrier()
+        arrived = torch.cuda.Event()
+        arrived.record(side)
+    for x in locals_:
+        x.record_stream(side)
+    own_planes()
+    return bufs, lease, arrived
 
 
 class _PeerReduce:
@@ -606,13 +637,37 @@ class _ShardedNA(torch.autograd.Function):
     def forward(ctx, q, k, v, extent, ks, dl, ca, scale, plans, rank, group, transport):
         peer = _use_peer(q, group, transport)
         lease = None
-        if peer:
-            (k_buf, v_buf), lease = exchange_halos_peer([k, v], plans, rank, group)
-        else:
-            k_buf, v_buf = exchange_halos([k, v], plans, rank, group)
-        slab = _slab(plans[rank], extent)
+        me = plans[rank]
+        slab = _slab(me, extent)
         one = (1,) * len(extent)
-        out, lse = _cuda.fused_forward(q, k_buf, v_buf, ks, one, dl, ca, scale, slab=slab)
+        below, above = me.q_lo - me.kv_lo, me.kv_hi - me.q_hi
+        planes = me.q_hi - me.q_lo
+        if peer and below + above > 0 and planes > below + above and q.shape[0] <= 8:
+            # The planes whose windows stay inside this rank's own planes are computed while the halo planes
+            # travel (copy engines and barriers on a second stream); the boundary planes follow.  A slab of
+            # several samples is not dense in memory, so the pieces are launched sample by sample.
+            (k_buf, v_buf), lease, arrived = exchange_halos_peer([k, v], plans, rank, group, aside=True)
+            q = q if q.is_contiguous() else q.contiguous()
+            out = torch.empty_like(q)
+            lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
+
+            def piece(p0, p1):
+                if p1 <= p0:
+                    return
+                part = _cuda.Slab(tuple(extent), (me.q_lo + p0,) + (0,) * (len(extent) - 1), slab.kv_offset)
+                for b in range(q.shape[0]):
+                    _cuda.fused_forward(q[b:b + 1, p0:p1], k_buf[b:b + 1], v_buf[b:b + 1], ks, one, dl, ca, scale, slab=part,
+                                        out=out[b:b + 1, p0:p1], lse=lse[b:b + 1, p0:p1])
+            piece(below, planes - above)
+            torch.cuda.current_stream(q.device).wait_event(arrived)
+            piece(0, below)
+            piece(planes - above, planes)
+        else:
+            if peer:
+                (k_buf, v_buf), lease = exchange_halos_peer([k, v], plans, rank, group)
+            else:
+                k_buf, v_buf = exchange_halos([k, v], plans, rank, group)
+            out, lse = _cuda.fused_forward(q, k_buf, v_buf, ks, one, dl, ca, scale, slab=slab)
         if lease is not None:
             lease.mark_read()
             if not lease.persistent and not any(ctx.needs_input_grad[:3]):

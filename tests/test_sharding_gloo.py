@@ -60,7 +60,7 @@ class _HostPeers:
         lease.keep = tensors
         return lease
 
-    def copy2d(self, dst, dst_pitch, src, src_pitch, width, rows):
+    def copy2d(self, dst, dst_pitch, src, src_pitch, width, rows, dma=False):
         import ctypes
         assert width % 16 == 0 and dst % 16 == 0 and src % 16 == 0
         for r in range(rows):
