@@ -621,6 +621,19 @@ def fused_slab_forward_backward(q, k_buf, v_buf, grad_out, plan: SlabPlan, exten
     return out, lse, dq, dk, dv
 
 
+def slab_forward_planes(q, k_buf, v_buf, out, lse, plan: SlabPlan, extent, ks, dl, ca, scale, p0: int, p1: int):
+    """The fused forward of the local query planes [p0, p1) of a slab, written into those planes of ``out`` and
+    ``lse``.  A range of planes of several samples is not dense in memory, so it is launched sample by sample."""
+    if p1 <= p0:
+        return
+    rank = len(extent)
+    part = _cuda.Slab(tuple(extent), (plan.q_lo + p0,) + (0,) * (rank - 1), (plan.kv_lo,) + (0,) * (rank - 1))
+    one = (1,) * rank
+    for b in range(q.shape[0]):
+        _cuda.fused_forward(q[b:b + 1, p0:p1], k_buf[b:b + 1], v_buf[b:b + 1], ks, one, dl, ca, scale, slab=part,
+                            out=out[b:b + 1, p0:p1], lse=lse[b:b + 1, p0:p1])
+
+
 def _tensor_core_slab(q, k_buf, ks, one, dl, ca, scale, slab) -> bool:
     """Whether the fused backward of this slab runs on the tensor-core kernels (which can deliver halo gradients)."""
     if q.dtype not in (torch.float16, torch.bfloat16) or _cuda.get_fused_path() == "simt":
@@ -650,18 +663,11 @@ class _ShardedNA(torch.autograd.Function):
             q = q if q.is_contiguous() else q.contiguous()
             out = torch.empty_like(q)
             lse = torch.empty(q.shape[:-1], dtype=torch.float32, device=q.device)
-
-            def piece(p0, p1):
-                if p1 <= p0:
-                    return
-                part = _cuda.Slab(tuple(extent), (me.q_lo + p0,) + (0,) * (len(extent) - 1), slab.kv_offset)
-                for b in range(q.shape[0]):
-                    _cuda.fused_forward(q[b:b + 1, p0:p1], k_buf[b:b + 1], v_buf[b:b + 1], ks, one, dl, ca, scale, slab=part,
-                                        out=out[b:b + 1, p0:p1], lse=lse[b:b + 1, p0:p1])
-            piece(below, planes - above)
+            args = (q, k_buf, v_buf, out, lse, me, extent, ks, dl, ca, scale)
+            slab_forward_planes(*args, below, planes - above)
             torch.cuda.current_stream(q.device).wait_event(arrived)
-            piece(0, below)
-            piece(planes - above, planes)
+            slab_forward_planes(*args, 0, below)
+            slab_forward_planes(*args, planes - above, planes)
         else:
             if peer:
                 (k_buf, v_buf), lease = exchange_halos_peer([k, v], plans, rank, group)

@@ -182,6 +182,33 @@ def test_leading_axis_slabs_on_the_tensor_core_kernels(shape, ks, dl, ca, world)
     assert _rel(dv_full, g_ref[2]) < 2e-2
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape,ks,dl,ca,world", [
+    ((2, 12, 9, 10, 2, 32), (3, 3, 5), (1, 1, 1), (True, False, False), 2),
+    ((2, 16, 12, 16, 4, 64), (5, 7, 3), (1, 1, 2), (False, False, False), 3),
+])
+def test_slab_forward_in_pieces(dtype, shape, ks, dl, ca, world):
+    """The forward of a slab launched as interior planes first and boundary planes afterwards, sample by sample
+    and into slices of the outputs (what the sharded forward does while the halo planes travel), equals the
+    one-launch forward of the slab."""
+    from natten_mlx_b200 import sharding
+    q, k, v = (_rand(shape, 400 + i, dtype).to(DEV) for i in range(3))
+    one = (1, 1, 1)
+    for r in range(world):
+        plan = sharding.slab_plan(shape[1], world, r, ks[0], dl[0], ca[0])
+        below, above, planes = plan.q_lo - plan.kv_lo, plan.kv_hi - plan.q_hi, plan.q_hi - plan.q_lo
+        qs = q[:, plan.q_lo:plan.q_hi].contiguous()
+        kb, vb = k[:, plan.kv_lo:plan.kv_hi].contiguous(), v[:, plan.kv_lo:plan.kv_hi].contiguous()
+        o_ref, l_ref = backend.fused_forward(qs, kb, vb, ks, one, dl, ca, None, slab=sharding._slab(plan, shape[1:4]))
+        out = torch.full_like(qs, float("nan"))
+        lse = torch.full(qs.shape[:-1], float("nan"), dtype=torch.float32, device=DEV)
+        for p0, p1 in ((below, planes - above), (0, below), (planes - above, planes)):
+            sharding.slab_forward_planes(qs, kb, vb, out, lse, plan, shape[1:4], ks, dl, ca, None, p0, p1)
+        tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+        assert _rel(out, o_ref) < tol and _rel(lse, l_ref) < tol / 10
+    assert _lib.kernel_status() == 0
+
+
 @pytest.mark.parametrize("shape,ks,dl,ca,world", [
     ((2, 12, 9, 10, 2, 32), (3, 3, 5), (1, 1, 1), (True, False, False), 2),
     ((2, 16, 12, 16, 4, 64), (5, 7, 3), (1, 1, 2), (False, False, False), 3),
